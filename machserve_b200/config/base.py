@@ -125,9 +125,12 @@ def known_architectures():
 
 
 def architecture_name(raw: Mapping[str, Any]) -> str:
+    """The name a config.json gives its model class: `architectures[0]`, or the string `architecture`."""
     archs = raw.get("architectures")
+    if archs is None and isinstance(raw.get("architecture"), str):
+        return raw["architecture"]
     if not isinstance(archs, list) or not archs or not isinstance(archs[0], str):
-        raise ConfigError("config.json: 'architectures' must be a list that names the model class")
+        raise ConfigError("config.json: 'architectures' must be a list that names the model class (or 'architecture' a string)")
     return archs[0]
 
 

@@ -44,14 +44,15 @@ class LayerSpec:
     """One layer: the arrangement (`block`) and the parts it arranges.
 
     `prefix` is the layer's tensor-name prefix; each part appends its own
-    tensor names to the prefix it is given.
+    tensor names to the prefix it is given.  A layer without a feed-forward
+    has None for it and for its norm; only blocks that say so take such a layer.
     """
 
     block: str
     mixer: PartSpec
-    feed_forward: PartSpec
+    feed_forward: Optional[PartSpec]
     mixer_norm: PartSpec
-    feed_forward_norm: PartSpec
+    feed_forward_norm: Optional[PartSpec]
     prefix: str
 
 
@@ -61,11 +62,14 @@ class RunSpec:
 
     `cache_of` is None when this run owns a cache of its own, or the index of
     an earlier entry of the run order whose cache this run reads (it then
-    writes nothing).
+    writes nothing).  `entry`, if given, is a part that rewrites the residual
+    stream right before this run (a `StreamEntry`: the start of a pass over a
+    looped range of layers, for instance).
     """
 
     layer: int
     cache_of: Optional[int] = None
+    entry: Optional[PartSpec] = None
 
 
 @dataclass(frozen=True)

@@ -1,0 +1,70 @@
+// Gated activations beside SiLU-mul: the clamped gated unit of a feed-forward, and a sigmoid gate on a mixer's output.
+//
+// clamped gated unit: gate_up is float32 [rows, 2*inter] (gate in columns [0, inter), up in [inter, 2*inter)), out the type
+// the next product reads;
+//   g = min(gate, limit), u = clamp(up, -limit, limit), out = g * sigmoid(alpha * g) * (u + shift).
+// sigmoid gate: out[r, c] = x[r, c] * sigmoid(gate[r, c]); x and gate are float32 with row strides of their own
+//   (a gate that is a column range of a wider product), out is the type the next product reads.
+// Both compute in float32 with the accurate expf.
+#include "launch.cuh"
+
+template <typename T>
+__global__ void glu_clamped_kernel(const float* __restrict__ gate_up, T* __restrict__ out, int inter, size_t total, float limit,
+                                   float alpha, float shift) {
+  ms_pdl_trigger();
+  ms_pdl_wait();
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const size_t r = i / inter;
+  const int c = (int)(i - r * inter);
+  const float g = fminf(gate_up[r * 2 * inter + c], limit);
+  const float u = fminf(fmaxf(gate_up[r * 2 * inter + inter + c], -limit), limit);
+  out[i] = ms_from_float<T>(g / (1.f + expf(-alpha * g)) * (u + shift));
+}
+
+MS_API int ms_glu_clamped(const float* gate_up, void* out, int dtype, int rows, int inter, float limit, float alpha, float shift,
+                          cudaStream_t stream) {
+  if (rows == 0) return 0;
+  MS_REQUIRE(rows > 0 && inter > 0 && limit > 0.f, "glu_clamped: bad arguments rows=%d inter=%d limit=%g", rows, inter, limit);
+  const size_t total = (size_t)rows * inter;
+  const unsigned blocks = (unsigned)((total + 255) / 256);
+  if (dtype == MS_F32)
+    MS_LAUNCH_RESULT("glu_clamped", ms_launch(glu_clamped_kernel<float>, dim3(blocks), dim3(256), 0, stream, 1, true,
+                                              gate_up, (float*)out, inter, total, limit, alpha, shift));
+  else if (dtype == MS_BF16)
+    MS_LAUNCH_RESULT("glu_clamped", ms_launch(glu_clamped_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, 1, true,
+                                              gate_up, (__nv_bfloat16*)out, inter, total, limit, alpha, shift));
+  else
+    MS_REQUIRE(false, "glu_clamped: unknown dtype %d", dtype);
+  return 0;
+}
+
+template <typename TO>
+__global__ void sigmoid_gate_mul_kernel(const float* __restrict__ x, int ldx, const float* __restrict__ gate, int ldg,
+                                        TO* __restrict__ out, int n, size_t total) {
+  ms_pdl_trigger();
+  ms_pdl_wait();
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const size_t r = i / n;
+  const int c = (int)(i - r * n);
+  const float g = gate[r * ldg + c];
+  out[i] = ms_from_float<TO>(x[r * ldx + c] / (1.f + expf(-g)));
+}
+
+MS_API int ms_sigmoid_gate_mul(const float* x, int ldx, const float* gate, int ldg, void* out, int out_dtype, int rows, int n,
+                               cudaStream_t stream) {
+  if (rows == 0) return 0;
+  MS_REQUIRE(rows > 0 && n > 0 && ldx >= n && ldg >= n, "sigmoid_gate_mul: bad sizes rows=%d n=%d", rows, n);
+  const size_t total = (size_t)rows * n;
+  const unsigned blocks = (unsigned)((total + 255) / 256);
+  if (out_dtype == MS_F32)
+    MS_LAUNCH_RESULT("sigmoid_gate_mul", ms_launch(sigmoid_gate_mul_kernel<float>, dim3(blocks), dim3(256), 0, stream, 1, true, x, ldx,
+                                                   gate, ldg, (float*)out, n, total));
+  else if (out_dtype == MS_BF16)
+    MS_LAUNCH_RESULT("sigmoid_gate_mul", ms_launch(sigmoid_gate_mul_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, 1, true,
+                                                   x, ldx, gate, ldg, (__nv_bfloat16*)out, n, total));
+  else
+    MS_REQUIRE(false, "sigmoid_gate_mul: unknown out dtype %d", out_dtype);
+  return 0;
+}

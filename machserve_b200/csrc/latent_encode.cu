@@ -1,0 +1,86 @@
+// What stands between the input product of a latent-attention mixer and its attention: the norm of the latent, the
+// rotation of the shared key part and of the queries' rotated parts, and the write of [latent | rotated key part]
+// into the one plane of pages that the mixer keeps.
+//
+// Row t of proj [T, ld], float32, holds the queries at column 0, head by head as [dn unrotated | dr rotated], and
+// at column kv_off the down-projection [r latent | dr key part].
+//   c  = latent / sqrt(mean(latent^2) + eps) * w            -> pages[.., 0:r]
+//   kr = turn(key part, p)                                   -> pages[.., r:r+dr]
+//   q_wide[t, h, r:r+dr] = turn(q[t, h, dn:dn+dr], p)        (float32; columns 0:r are filled by the product of the
+//                                                             unrotated queries with the keys' up-projection)
+//   q_plain[t, h, :] = q[t, h, 0:dn]                          (in the type that product reads)
+// turn: the pair (2i, 2i+1), i < rot/2, at position p becomes (u cos a - v sin a, v cos a + u sin a) with (cos a, sin a)
+// from the table [positions, rot/2, 2]; coordinates from `rot` on pass unchanged.  Rows without a request (slot < 0)
+// are passed over.  float32 arithmetic throughout.
+#include "launch.cuh"
+
+__device__ __forceinline__ float latent_turn(const float* x, int e, int rot, const float* cs) {
+  if (e >= rot) return x[e];
+  const int i = e >> 1;
+  const float c = cs[2 * i], s = cs[2 * i + 1];
+  const float u = x[2 * i], v = x[2 * i + 1];
+  return (e & 1) ? v * c + u * s : u * c - v * s;
+}
+
+template <typename TC, typename TN>
+__global__ void __launch_bounds__(256)
+latent_encode_kernel(const float* __restrict__ proj, int ld, int kv_off, const float* __restrict__ w_latent, float eps,
+                     const float* __restrict__ cos_sin, int rot, const int* __restrict__ positions,
+                     const int* __restrict__ slots, const int* __restrict__ block_table, int max_pages, int num_pages,
+                     int page_size, float* __restrict__ q_wide, TN* __restrict__ q_plain, TC* __restrict__ pages, int heads,
+                     int dn, int dr, int r, int store) {
+  __shared__ float scratch[33];
+  ms_pdl_trigger();
+  ms_pdl_wait();
+  const int t = blockIdx.x;
+  const int slot = slots[t];
+  if (slot < 0) return;
+  const int pos = positions[t];
+  const float* row = proj + (size_t)t * ld;
+  const float* cs = cos_sin + (size_t)pos * rot;  // [rot/2][2]
+  const int hd = dn + dr, wide = r + dr;
+  for (int c = threadIdx.x; c < heads * hd; c += blockDim.x) {
+    const int h = c / hd, e = c - h * hd;
+    if (e < dn)
+      q_plain[((size_t)t * heads + h) * dn + e] = ms_from_float<TN>(row[c]);
+    else
+      q_wide[((size_t)t * heads + h) * wide + r + (e - dn)] = latent_turn(row + h * hd + dn, e - dn, rot, cs);
+  }
+  if (!store) return;
+  const float* kv = row + kv_off;
+  float ss = 0.f;
+  for (int c = threadIdx.x; c < r; c += blockDim.x) ss += kv[c] * kv[c];
+  const float inv = 1.f / sqrtf(ms_block_sum(ss, scratch) / (float)r + eps);
+  const int page = block_table[(size_t)slot * max_pages + pos / page_size];
+  if (page < 0 || page >= num_pages) return;
+  TC* dst = pages + ((size_t)page * page_size + pos % page_size) * wide;
+  for (int c = threadIdx.x; c < wide; c += blockDim.x)
+    dst[c] = ms_from_float<TC>(c < r ? kv[c] * inv * w_latent[c] : latent_turn(kv + r, c - r, rot, cs));
+}
+
+MS_API int ms_latent_encode(const float* proj, int ld, int kv_off, const float* w_latent, float eps, const float* cos_sin,
+                            int rot, int table_positions, const int* positions, const int* slots, const int* block_table,
+                            int max_pages, int num_pages, int page_size, float* q_wide, void* q_plain, int plain_dtype,
+                            void* pages, int cache_dtype, int tokens, int heads, int dn, int dr, int r, int store,
+                            cudaStream_t stream) {
+  if (tokens == 0) return 0;
+  MS_REQUIRE(tokens > 0 && heads > 0 && dn > 0 && dr >= 0 && r > 0, "latent_encode: bad sizes");
+  MS_REQUIRE(rot >= 0 && rot <= dr && rot % 2 == 0, "latent_encode: %d rotated coordinates of %d", rot, dr);
+  MS_REQUIRE(rot == 0 || (cos_sin && table_positions > 0), "latent_encode: no table of angles");
+  MS_REQUIRE(ld >= heads * (dn + dr) && ld >= kv_off + (store ? r + dr : 0), "latent_encode: rows of %d elements are too short", ld);
+  MS_REQUIRE(!store || (max_pages > 0 && num_pages > 0 && page_size > 0 && pages), "latent_encode: no cache to write");
+#define MS_LATENT(TC, TN)                                                                                                 \
+  MS_LAUNCH_RESULT("latent_encode", ms_launch(latent_encode_kernel<TC, TN>, dim3(tokens), dim3(256), 0, stream, 1, true, proj, ld, \
+                                              kv_off, w_latent, eps, cos_sin, rot, positions, slots, block_table, max_pages,      \
+                                              num_pages, page_size, q_wide, (TN*)q_plain, (TC*)pages, heads, dn, dr, r, store))
+  if (cache_dtype == MS_F32 && plain_dtype == MS_F32)
+    MS_LATENT(float, float);
+  else if (cache_dtype == MS_BF16 && plain_dtype == MS_BF16)
+    MS_LATENT(__nv_bfloat16, __nv_bfloat16);
+  else if (cache_dtype == MS_BF16 && plain_dtype == MS_F32)
+    MS_LATENT(__nv_bfloat16, float);
+  else
+    MS_REQUIRE(false, "latent_encode: unsupported dtypes cache=%d queries=%d", cache_dtype, plain_dtype);
+#undef MS_LATENT
+  return 0;
+}

@@ -623,8 +623,7 @@ class ModelRunner:
 
 def _unique_tensors(model):
     seen, out = set(), []
-    parts = [model.embedding, *[p for b in model.blocks for p in b.parts()], model.final_norm, model.head]
-    for part in parts:
+    for part in model.parts():
         for v in vars(part).values():
             if isinstance(v, torch.Tensor) and v.data_ptr() not in seen:
                 seen.add(v.data_ptr())

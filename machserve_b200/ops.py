@@ -69,6 +69,13 @@ class _Signatures:
     ms_add_rmsnorm = [P, P, I, P, P, I, P, I, I, F, P]
     ms_add_bias = [P, I, P, I, I, I, P]
     ms_silu_mul = [P, P, I, I, I, P]
+    ms_add_layernorm = [P, P, I, P, I, P, P, P, P, P, P, I, P, I, I, F, P]
+    ms_concat_streams = [P, P, I, P, I, P, P, I, I, I, P]
+    ms_glu_clamped = [P, P, I, I, I, F, F, F, P]
+    ms_sigmoid_gate_mul = [P, I, P, I, P, I, I, I, P]
+    ms_qk_norm_store = [P, I, P, P, F, F, I, P, P, P, I, I, I, P, P, P, I, I, I, I, I, I, I, P]
+    ms_latent_encode = [P, I, I, P, F, P, I, I, P, P, P, I, I, I, P, P, I, P, I, I, I, I, I, I, I, P]
+    ms_attention_wide = [P, P, P, P, I, P, P, P, P, I, I, I, I, I, I, I, I, I, I, F, I, P]
     ms_rope_kv_store = [P, I, I, P, P, P, P, I, I, P, I, I, P, P, P, I, I, I, I, I, I, P]
     ms_attention_generic = [P, P, P, P, I, I, P, P, P, I, I, I, I, I, I, I, I, F, I, P]
     ms_gemm_f32 = [P, I, P, P, P, I, I, I, I, P]
@@ -852,6 +859,169 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: 
     else:
         torch.mm(x, w.t(), out_dtype=torch.float32, out=out)
     return add_bias(out, bias) if bias is not None else out
+
+
+
+# ------------------------------------------------------------------- parts of layers beyond the pre-norm decoder's
+
+
+def _delta_args(delta):
+    return (_ptr(delta), _code(delta) if delta is not None else F32)
+
+
+def add_layernorm(residual, delta_a, delta_b, weight, bias, out, eps, rows=None, weight2=None, bias2=None, out2=None):
+    """out = layernorm(residual + (delta_a + delta_b)) * weight + bias (mean and variance of the row, eps inside the
+    root); without `rows` the sum is written back to `residual`.  With weight2, bias2 and out2 a second norm of the same
+    rows is written beside the first (they share mean and variance).
+
+    residual float32 [T, d]; deltas [T, d] float32 or bfloat16 or None; weights and biases float32 [d];
+    out, out2 [n_out, d]; rows int32 [n_out] picks input rows (then nothing is written back)."""
+    d = residual.shape[1]
+    n_out = out.shape[0]
+    _need(residual.dtype == torch.float32 and residual.is_contiguous() and out.is_contiguous() and out.shape[1] == d,
+          "add_layernorm: bad layout")
+    for v in (weight, bias, weight2, bias2):
+        _need(v is None or (v.dtype == torch.float32 and v.numel() == d and v.is_contiguous()), "add_layernorm: bad weight or bias")
+    for dl in (delta_a, delta_b):
+        _need(dl is None or (dl.shape[1] == d and dl.is_contiguous() and dl.shape[0] >= residual.shape[0]), "add_layernorm: bad delta")
+    if out2 is not None:
+        _need(weight2 is not None and bias2 is not None and out2.dtype == out.dtype and out2.is_contiguous()
+              and tuple(out2.shape) == tuple(out.shape), "add_layernorm: bad second norm")
+    if rows is None:
+        _need(n_out == residual.shape[0], "add_layernorm: out must have the residual's rows")
+    else:
+        _need(rows.dtype == torch.int32 and rows.numel() >= n_out, "add_layernorm: bad row list")
+    _check(lib().ms_add_layernorm(_ptr(residual), *_delta_args(delta_a), *_delta_args(delta_b), _ptr(weight), _ptr(bias), _ptr(out),
+                                  _ptr(weight2), _ptr(bias2), _ptr(out2), _code(out), _ptr(rows), n_out, d, float(eps), _stream()),
+           "add_layernorm")
+    return out
+
+
+def concat_streams(residual, delta_a, delta_b, other, out):
+    """out[:, :d] = residual + (delta_a + delta_b), out[:, d:] = other: residual and other float32 [T, d], out [T, 2d]."""
+    t, d = residual.shape
+    _need(residual.dtype == torch.float32 and other.dtype == torch.float32 and residual.is_contiguous() and other.is_contiguous()
+          and tuple(other.shape) == (t, d) and tuple(out.shape) == (t, 2 * d) and out.is_contiguous(), "concat_streams: bad arguments")
+    for dl in (delta_a, delta_b):
+        _need(dl is None or (dl.shape[1] == d and dl.is_contiguous() and dl.shape[0] >= t), "concat_streams: bad delta")
+    _check(lib().ms_concat_streams(_ptr(residual), *_delta_args(delta_a), *_delta_args(delta_b), _ptr(other), _ptr(out), _code(out),
+                                   t, d, _stream()), "concat_streams")
+    return out
+
+
+def glu_clamped(gate_up, out, limit: float, alpha: float, shift: float):
+    """out = g * sigmoid(alpha * g) * (u + shift) with g = min(gate, limit), u = clamp(up, -limit, limit);
+    gate_up float32 [R, 2*inter] (gate first), out [R, inter] float32 or bfloat16."""
+    rows, inter = out.shape
+    _need(gate_up.shape[1] == 2 * inter and gate_up.dtype == torch.float32 and gate_up.is_contiguous() and out.is_contiguous(),
+          "glu_clamped: bad arguments")
+    _check(lib().ms_glu_clamped(_ptr(gate_up), _ptr(out), _code(out), rows, inter, float(limit), float(alpha), float(shift), _stream()),
+           "glu_clamped")
+    return out
+
+
+def sigmoid_gate_mul(x, gate, out):
+    """out = x * sigmoid(gate): x and gate float32 [R, n] with unit column stride (any row stride), out [R, n] contiguous."""
+    rows, n = out.shape
+    _need(x.dtype == torch.float32 and gate.dtype == torch.float32 and x.stride(1) == 1 and gate.stride(1) == 1
+          and tuple(x.shape) == (rows, n) and tuple(gate.shape) == (rows, n) and out.is_contiguous(), "sigmoid_gate_mul: bad arguments")
+    _check(lib().ms_sigmoid_gate_mul(_ptr(x), x.stride(0), _ptr(gate), gate.stride(0), _ptr(out), _code(out), rows, n, _stream()),
+           "sigmoid_gate_mul")
+    return out
+
+
+def qk_norm_store(proj, wq, wk, eps, coef, every, positions, slot_of_token, block_table, q_out, k_pages, v_pages,
+                  groups: int, dk: int, dv: int, store: bool = True):
+    """Unit-rms norm of the whole q and of the whole k projection with weights, query temperature
+    1 + coef * ln(floor((p + 1) / every) + 1), q to q_out (float32), k and v into their pages.
+
+    proj float32 [T, >= qw + groups*(dk + dv)] = [q | k | v]; wq [qw], wk [groups*dk] float32; q_out float32 [T, qw];
+    k pages [pages, groups, page, dk], v pages [pages, groups, page, dv]."""
+    t, qw = q_out.shape
+    _need(proj.dtype == torch.float32 and proj.stride(1) == 1 and q_out.dtype == torch.float32 and q_out.is_contiguous(),
+          "qk_norm_store: bad layout")
+    _need(wq.dtype == torch.float32 and wq.numel() == qw and wk.dtype == torch.float32 and wk.numel() == groups * dk,
+          "qk_norm_store: bad norm weights")
+    if store:
+        _need(k_pages.is_contiguous() and v_pages.is_contiguous() and k_pages.dtype == v_pages.dtype
+              and tuple(k_pages.shape[1:]) == (groups, k_pages.shape[2], dk) and tuple(v_pages.shape[1:]) == (groups, k_pages.shape[2], dv),
+              "qk_norm_store: bad pages")
+        _need(block_table.dtype == torch.int32 and block_table.is_contiguous(), "qk_norm_store: bad block table")
+    _check(lib().ms_qk_norm_store(
+        _ptr(proj), proj.stride(0), _ptr(wq), _ptr(wk), float(eps), float(coef), int(every), _ptr(positions), _ptr(slot_of_token),
+        _ptr(block_table), block_table.shape[1] if store else 0, k_pages.shape[0] if store else 0, k_pages.shape[2] if store else 0,
+        _ptr(q_out), _ptr(k_pages if store else None), _ptr(v_pages if store else None), _code(k_pages) if store else F32,
+        t, qw, groups, dk, dv, int(store), _stream()), "qk_norm_store")
+    return q_out
+
+
+def latent_encode(proj, kv_off, w_latent, eps, cos_sin, rot, positions, slot_of_token, block_table, q_wide, q_plain, pages,
+                  heads: int, dn: int, dr: int, r: int, store: bool = True):
+    """Between the input product of a latent-attention mixer and its attention: the latent's unit-rms norm with weight
+    and the rotated key part into the pages [pages, 1, page, r + dr]; the queries' rotated parts into q_wide[:, :, r:]
+    (float32 [T, heads, r + dr]); their unrotated parts into q_plain [T, heads, dn] (the dtype their product reads).
+
+    proj float32 [T, ld]: queries at column 0 head by head as [dn | dr], the down-projection [r | dr] at `kv_off`;
+    cos_sin float32 [positions, rot/2, 2]: interleaved pairs of the first `rot` of the dr coordinates are turned."""
+    t = q_plain.shape[0]
+    _need(proj.dtype == torch.float32 and proj.stride(1) == 1 and q_wide.dtype == torch.float32 and q_wide.is_contiguous()
+          and q_plain.is_contiguous() and q_wide.numel() == t * heads * (r + dr) and q_plain.numel() == t * heads * dn,
+          "latent_encode: bad layout")
+    _need(w_latent.dtype == torch.float32 and w_latent.numel() == r, "latent_encode: bad norm weight")
+    if rot:
+        _need(cos_sin is not None and cos_sin.dtype == torch.float32 and cos_sin.is_contiguous() and cos_sin.shape[1] * 2 == rot,
+              "latent_encode: bad table of angles")
+    if store:
+        _need(pages.is_contiguous() and tuple(pages.shape[1:]) == (1, pages.shape[2], r + dr), "latent_encode: bad pages")
+        _need(block_table.dtype == torch.int32 and block_table.is_contiguous(), "latent_encode: bad block table")
+    _check(lib().ms_latent_encode(
+        _ptr(proj), proj.stride(0), int(kv_off), _ptr(w_latent), float(eps), _ptr(cos_sin), int(rot),
+        cos_sin.shape[0] if cos_sin is not None else 0, _ptr(positions), _ptr(slot_of_token), _ptr(block_table),
+        block_table.shape[1] if store else 0, pages.shape[0] if store else 0, pages.shape[2] if store else 0, _ptr(q_wide),
+        _ptr(q_plain), _code(q_plain), _ptr(pages if store else None), _code(pages) if store else _code(q_plain), t, heads, dn, dr, r,
+        int(store), _stream()), "latent_encode")
+    return q_wide
+
+
+def attention_wide(q, k_pages, v_pages, out, sinks, positions, slot_of_token, block_table, num_heads: int, num_kv_heads: int,
+                   dk: int, dv: int, window: Optional[int], scale: float, share_rows: bool = False):
+    """The exact paged attention for keys and values of different widths, with an optional sink per head in the
+    softmax's denominator.  q float32 [T, Hq*dk]; k pages [pages, Hkv, page, dk]; v pages [pages, Hkv, page, vw] of which
+    the first dv columns are the values (the same array as the keys for a latent cache); out [T, Hq*dv] in the cache's
+    dtype; sinks float32 [Hq] or None.  `share_rows` as in attention_generic: the same bits either way."""
+    tokens = q.shape[0]
+    _need(q.dtype == torch.float32 and q.is_contiguous() and out.is_contiguous() and out.dtype == k_pages.dtype
+          and q.numel() == tokens * num_heads * dk and out.numel() == tokens * num_heads * dv, "attention_wide: bad layout")
+    _need(k_pages.is_contiguous() and v_pages.is_contiguous() and k_pages.dtype == v_pages.dtype, "attention_wide: bad pages")
+    _need(tuple(k_pages.shape[1:]) == (num_kv_heads, k_pages.shape[2], dk) and tuple(v_pages.shape[:3]) == tuple(k_pages.shape[:3])
+          and v_pages.shape[3] >= dv, "attention_wide: bad page shapes")
+    _need(sinks is None or (sinks.dtype == torch.float32 and sinks.numel() == num_heads), "attention_wide: bad sinks")
+    _need(block_table.dtype == torch.int32 and block_table.is_contiguous(), "attention_wide: bad block table")
+    _check(lib().ms_attention_wide(
+        _ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(out), _code(k_pages), _ptr(sinks), _ptr(positions), _ptr(slot_of_token),
+        _ptr(block_table), block_table.shape[1], k_pages.shape[0], tokens, num_heads, num_kv_heads, dk, dv, v_pages.shape[3],
+        k_pages.shape[2], int(window or 0), float(scale), int(share_rows), _stream()), "attention_wide")
+    return out
+
+
+def linear_heads(x, w, out):
+    """out[:, h, :] = x[:, h, :] . w[h]^T for every head h: x [T, H, a] and out [T, H, b] with unit stride along the last
+    axis (any strides otherwise), w [H, b, a] contiguous.  float32 operands: one CUDA-core product per head (row results
+    independent of the batch); bfloat16 operands: the library's batched product, out float32 or bfloat16."""
+    t, heads, a = x.shape
+    b = w.shape[1]
+    _need(tuple(w.shape) == (heads, b, a) and w.is_contiguous() and tuple(out.shape) == (t, heads, b)
+          and x.stride(2) == 1 and out.stride(2) == 1, "linear_heads: bad layout")
+    if x.dtype == torch.float32:
+        for h in range(heads):
+            gemm_f32(x[:, h], w[h], None, out[:, h])
+        return out
+    _need(x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16, "linear_heads: operands must both be bfloat16 or float32")
+    if out.dtype == torch.bfloat16:
+        torch.bmm(x.transpose(0, 1), w.transpose(1, 2), out=out.transpose(0, 1))
+    else:
+        torch.bmm(x.transpose(0, 1), w.transpose(1, 2), out_dtype=torch.float32, out=out.transpose(0, 1))
+    return out
 
 
 def apply_logit_offsets(logits, row_ptr, tokens, amounts):

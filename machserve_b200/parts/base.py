@@ -164,9 +164,23 @@ class RowStats:
     copy: Optional[torch.Tensor] = None  # the residual rounded to the runtime's dtype, if its producer left one
 
 
-def as_delta(pending):
-    """What a norm adds to the residual before it normalises: a `RowStats` says that the add has been done."""
-    return None if isinstance(pending, RowStats) else pending
+@dataclass
+class DeltaPair:
+    """Two deltas that a block hands on together (a parallel layer's mixer and feed-forward outputs): the stream gets
+    stream + (a + b).  A norm that sets `accepts_pairs` adds them itself; for every other part `as_delta` sums them."""
+
+    a: torch.Tensor
+    b: torch.Tensor
+
+
+def as_delta(pending, pairs: bool = False):
+    """What a norm adds to the residual before it normalises: a `RowStats` says that the add has been done; a
+    `DeltaPair` is summed (in float32) unless the caller takes pairs."""
+    if isinstance(pending, RowStats):
+        return None
+    if isinstance(pending, DeltaPair) and not pairs:
+        return pending.a.float() + pending.b.float()
+    return pending
 
 
 # ------------------------------------------------------------------- work plans
@@ -285,6 +299,8 @@ class Norm(Part):
       With `rows` (int32 indices), out[i] = norm(residual[rows[i]] + delta[rows[i]]) and nothing is written back.
     """
 
+    accepts_pairs = False  # True: `delta` may also be a `DeltaPair`, whose sum the norm adds
+
     def forward(self, residual, delta, out, rows=None):
         raise NotImplementedError
 
@@ -339,6 +355,19 @@ class FeedForward(Part):
         raise NotImplementedError
 
 
+class StreamEntry(Part):
+    """Rewrites the residual stream between two runs of layers, for all rows of the step.
+
+    forward(ctx, residual, pending, first) -> pending: `residual` is the float32 stream [T, hidden] with `pending`
+    (a delta, a `DeltaPair` or None) not yet added to it; `first` is the stream as the embedding left it (float32
+    [T, hidden], not to be written).  The part leaves the new stream in `residual` and returns what is still to be
+    added (usually None).  Named by `RunSpec.entry`, it runs right before that run's layer.
+    """
+
+    def forward(self, ctx, residual, pending, first):
+        raise NotImplementedError
+
+
 class Block:
     """The arrangement of a layer's parts around the residual stream.
 
@@ -350,12 +379,16 @@ class Block:
     """
 
     accepts_row_stats = False
+    accepts_pairs = False  # True: `pending` may also be a `DeltaPair`
+    optional_feed_forward = False  # True: the block also arranges a layer that has no feed-forward
 
-    def __init__(self, spec: LayerSpec, mixer: Mixer, feed_forward: FeedForward, mixer_norm: Norm, ff_norm: Norm):
+    def __init__(self, spec: LayerSpec, mixer: Mixer, feed_forward: Optional[FeedForward], mixer_norm: Norm, ff_norm: Optional[Norm]):
         self.spec, self.mixer, self.feed_forward, self.mixer_norm, self.ff_norm = spec, mixer, feed_forward, mixer_norm, ff_norm
+        if feed_forward is None and not self.optional_feed_forward:
+            raise ValueError(f"a block of kind '{spec.block}' needs a feed-forward")
 
     def parts(self) -> List[Part]:
-        return [self.mixer_norm, self.mixer, self.ff_norm, self.feed_forward]
+        return [p for p in (self.mixer_norm, self.mixer, self.ff_norm, self.feed_forward) if p is not None]
 
     def bind(self, tensors: Dict[str, torch.Tensor], rt: Runtime) -> None:
         for p in self.parts():
@@ -396,6 +429,7 @@ FEED_FORWARDS = _Registry("feed-forward")
 NORMS = _Registry("norm")
 POSITION_ENCODINGS = _Registry("position encoding")
 BLOCKS = _Registry("block")
+STREAM_ENTRIES = _Registry("stream entry")
 
 register_embedding = EMBEDDINGS.register
 register_head = HEADS.register
@@ -404,6 +438,7 @@ register_feed_forward = FEED_FORWARDS.register
 register_norm = NORMS.register
 register_position_encoding = POSITION_ENCODINGS.register
 register_block = BLOCKS.register
+register_stream_entry = STREAM_ENTRIES.register
 
 
 def vector_f32(t: torch.Tensor) -> torch.Tensor:

@@ -1,7 +1,7 @@
 """Arrangements of a layer's parts around the residual stream."""
 from __future__ import annotations
 
-from .base import Block, as_delta, register_block
+from .base import Block, DeltaPair, as_delta, register_block
 
 
 @register_block("prenorm")
@@ -44,3 +44,38 @@ class PreNormBlock(Block):
         xn = rt.workspace.get("block.normed", (t, d), rt.dtype)
         self.ff_norm.forward(residual, as_delta(pending), xn)
         return self.feed_forward.forward(ctx, xn)
+
+
+@register_block("parallel")
+class ParallelBlock(Block):
+    """x += mixer(norm1(x)) + feed_forward(norm2(x)): both norms read the same x, and the two outputs are summed before
+    they are added to the stream.  The block hands both on (`DeltaPair`); the next norm adds them in float32.  Two layer
+    norms of equal size and eps share their mean and variance and are written by one kernel.  A layer without a
+    feed-forward is x += mixer(norm1(x)).
+    """
+
+    graph_safe = True
+    accepts_pairs = True
+    optional_feed_forward = True
+
+    def bind(self, tensors, rt):
+        super().bind(tensors, rt)
+        both = getattr(self.mixer_norm, "shares_statistics_with", None)
+        self.one_kernel = self.ff_norm is not None and both is not None and both(self.ff_norm)
+
+    def forward(self, ctx, residual, pending, cache, owns_cache=True):
+        rt = ctx.rt
+        t, d = residual.shape
+        pairs = self.mixer_norm.accepts_pairs
+        xn = rt.workspace.get("block.normed", (t, d), rt.dtype)
+        if self.feed_forward is None:
+            self.mixer_norm.forward(residual, as_delta(pending, pairs), xn)
+            return self.mixer.forward(ctx, xn, cache, owns_cache)
+        xf = rt.workspace.get("block.normed_ff", (t, d), rt.dtype)
+        if self.one_kernel:
+            self.mixer_norm.forward_both(self.ff_norm, residual, as_delta(pending, pairs), xn, xf)
+        else:
+            self.mixer_norm.forward(residual, as_delta(pending, pairs), xn)
+            self.ff_norm.forward(residual, None, xf)
+        a = self.mixer.forward(ctx, xn, cache, owns_cache)
+        return DeltaPair(a, self.feed_forward.forward(ctx, xf))

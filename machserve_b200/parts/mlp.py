@@ -1,4 +1,4 @@
-"""The dense gated feed-forward (SwiGLU)."""
+"""The dense gated feed-forwards: SwiGLU, and the clamped gated unit."""
 from __future__ import annotations
 
 import torch
@@ -89,4 +89,44 @@ class SwiGLU(FeedForward):
             ops.linear(x, self.w_gate_up, None, gate_up)
             ops.silu_mul(gate_up, h)
         delta = ws.get("ffn.delta", (t, self.hidden), rt.dtype)
+        return ops.linear(h, self.w_down, None, delta)
+
+
+@register_feed_forward("clamped_glu")
+class ClampedGLU(FeedForward):
+    """delta = down(g * sigmoid(alpha * g) * (u + shift)) with g = min(gate(x), limit), u = clamp(up(x), -limit, limit);
+    no biases.  gate and up are one matrix product over the concatenated weights, with a float32 result (the clamps
+    and the gate are computed in float32); the delta is float32.
+
+    params: prefix, hidden_size, intermediate_size, limit, alpha (1.702 if absent), shift (1 if absent), and the three
+    tensor names under the prefix: gate, up, down (`gate`, `up`, `down` if absent).
+    """
+
+    graph_safe = True
+
+    def __init__(self, spec):
+        super().__init__(spec)
+        self.prefix = spec["prefix"]
+        self.hidden, self.inter = int(spec["hidden_size"]), int(spec["intermediate_size"])
+        self.limit, self.alpha, self.shift = float(spec["limit"]), float(spec.get("alpha", 1.702)), float(spec.get("shift", 1.0))
+        self.names = tuple(self.prefix + spec.get(k, k) for k in ("gate", "up", "down"))
+
+    def tensors(self):
+        g, u, d = self.names
+        return [TensorDecl(g, (self.inter, self.hidden)), TensorDecl(u, (self.inter, self.hidden)), TensorDecl(d, (self.hidden, self.inter))]
+
+    def bind(self, tensors, rt):
+        super().bind(tensors, rt)
+        g, u, d = self.names
+        self.w_gate_up = matrix(torch.cat([tensors[g], tensors[u]], dim=0), rt)
+        self.w_down = matrix(tensors[d], rt)
+
+    def forward(self, ctx, x):
+        rt, t = self.rt, x.shape[0]
+        ws = rt.workspace
+        gate_up = ws.get("ffn.gate_up_f32", (t, 2 * self.inter), torch.float32)
+        ops.linear(x, self.w_gate_up, None, gate_up)
+        h = ws.get("ffn.h", (t, self.inter), rt.dtype)
+        ops.glu_clamped(gate_up, h, self.limit, self.alpha, self.shift)
+        delta = ws.get("ffn.delta_f32", (t, self.hidden), torch.float32)
         return ops.linear(h, self.w_down, None, delta)

@@ -12,7 +12,8 @@ import torch
 
 from ..config.spec import LayerSpec, ModelSpec
 from ..weights.loader import TensorDecl
-from .base import BLOCKS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS, Block, CacheNeed, Part, Runtime, as_delta
+from .base import (BLOCKS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS, STREAM_ENTRIES, Block, CacheNeed, DeltaPair, Part, Runtime,
+                   as_delta)
 
 
 def build_block(layer: LayerSpec) -> Block:
@@ -22,9 +23,9 @@ def build_block(layer: LayerSpec) -> Block:
     return cls(
         layer,
         MIXERS.build(layer.mixer),
-        FEED_FORWARDS.build(layer.feed_forward),
+        FEED_FORWARDS.build(layer.feed_forward) if layer.feed_forward is not None else None,
         NORMS.build(layer.mixer_norm),
-        NORMS.build(layer.feed_forward_norm),
+        NORMS.build(layer.feed_forward_norm) if layer.feed_forward_norm is not None else None,
     )
 
 
@@ -33,6 +34,8 @@ class DecoderModel:
         self.spec = spec
         self.embedding = EMBEDDINGS.build(spec.embedding)
         self.blocks: List[Block] = [build_block(l) for l in spec.layers]
+        # parts that rewrite the stream right before a run (`RunSpec.entry`), by the run's place in the order
+        self.entries = {i: STREAM_ENTRIES.build(run.entry) for i, run in enumerate(spec.run_order) if run.entry is not None}
         self.final_norm = NORMS.build(spec.final_norm)
         self.head = HEADS.build(spec.head)
         self.rt: Optional[Runtime] = None
@@ -54,7 +57,7 @@ class DecoderModel:
         return out
 
     def parts(self) -> List[Part]:
-        return [self.embedding, *[p for b in self.blocks for p in b.parts()], self.final_norm, self.head]
+        return [self.embedding, *[p for b in self.blocks for p in b.parts()], *self.entries.values(), self.final_norm, self.head]
 
     def cache_needs(self) -> List[CacheNeed]:
         """For every entry of the run order: the cache its run owns, or None if it owns none."""
@@ -83,6 +86,8 @@ class DecoderModel:
         self.embedding.bind(tensors, rt)
         for b in self.blocks:
             b.bind(tensors, rt)
+        for e in self.entries.values():
+            e.bind(tensors, rt)
         self.final_norm.bind(tensors, rt)
         self.head.bind(tensors, rt, self.embedding)
 
@@ -103,18 +108,26 @@ class DecoderModel:
         self.embedding.forward(ctx, residual)
         if tap is not None:
             tap(-1, residual.clone())
+        first = None
+        if self.entries:  # the stream as the embedding left it, for the parts that read it again later
+            first = ws.get("model.embedding_out", (t, spec.hidden_size), torch.float32)
+            first.copy_(residual)
         pending = None
         for i, run in enumerate(spec.run_order):
             block = self.blocks[run.layer]
-            if not block.accepts_row_stats:
-                pending = as_delta(pending)  # a block of another kind sees a delta or None, as every norm does
+            if i in self.entries:
+                pending = self.entries[i].forward(ctx, residual, pending, first)
+            if not block.accepts_row_stats:  # a block of another kind sees a delta or None, as every norm does
+                pending = as_delta(pending, pairs=block.accepts_pairs)
+            elif isinstance(pending, DeltaPair):
+                pending = as_delta(pending)
             pending = block.forward(ctx, residual, pending, caches[i], run.cache_of is None)
             if tap is not None:  # the delta a block hands on is part of the hidden rows after it
                 delta = as_delta(pending)
                 tap(i, residual.clone() if delta is None else residual + delta[: residual.shape[0]].float())
         w = ctx.want_rows.shape[0]
         final = ws.get("model.final", (w, spec.hidden_size), rt.dtype)
-        self.final_norm.forward(residual, as_delta(pending), final, rows=ctx.want_rows)
+        self.final_norm.forward(residual, as_delta(pending, pairs=self.final_norm.accepts_pairs), final, rows=ctx.want_rows)
         logits = ws.get("model.logits", (w, spec.vocab_size), torch.float32)
         return self.head.forward(ctx, final, logits)
 
