@@ -26,6 +26,11 @@ Beside the headline the default run measures, under keys of their own:
 * `mixed_7b`: Qwen2.5-7B sizes, one step of eight 512-row portions of 4,096-token prompts
   (3,584 earlier tokens in the cache) beside 56 decoding rows at 1,024-token contexts.
 
+`--only venarax` (not part of the default run) times the Venarax design (parallel layers, attention with a sink,
+latent attention, clamped gated feed-forward) at the layer sizes of the three Qwen2.5 shapes beside the dense decoder
+at the same sizes: decode at `--batch` and `--context`, one prompt of `--prefill` tokens, and the design's kernels
+alone beside the like kernels of the dense decoder, each with its fraction of the measured peak.
+
 This engine runs on one GPU: for --gpus > 1 it says so and exits with 2.
 
     python bench.py --kernel attention_prefill
@@ -294,7 +299,7 @@ def time_attention_prefill(torch, ops, a, pk) -> int:
 class DecodeBench:
     """A runner of one shape with helpers that fill contexts and time decode steps and a prefill."""
 
-    def __init__(self, a, raw, layers, dtype, max_batch, max_seq, load_dir=None):
+    def __init__(self, a, raw, layers, dtype, max_batch, max_seq, load_dir=None, config=None, vocab=None):
         import numpy as np
         import torch
 
@@ -309,13 +314,15 @@ class DecodeBench:
                   max_step_tokens=2048 + max_batch, max_seq_len=max_seq)
         if load_dir:
             self.runner = ModelRunner.from_model_dir(load_dir, **kw)
+        elif config is not None:  # a configuration of any architecture, as its config.json would give it
+            self.runner = ModelRunner.from_random(config_from_json(config), seed=0, on_device=True, **kw)
         else:
             cfg = dict(raw)
             cfg["num_hidden_layers"] = layers
             self.runner = ModelRunner.from_random(config_from_json(cfg), seed=0, on_device=True, **kw)
         self.sampler = Sampler(max_batch, self.runner.device)
         self.rng = np.random.default_rng(0)
-        self.vocab = raw["vocab_size"]
+        self.vocab = vocab or raw["vocab_size"]
 
     def release_all(self):
         for r in list(self.runner.cache.requests):
@@ -455,6 +462,179 @@ def workload_fp32(a, pk, raw, layers):
     del b
     free_device_memory()
     return out
+
+
+def venarax_config(raw, layers, window=1024):
+    """A Venarax configuration with the layer sizes of the Qwen2 shape `raw`: the same width, heads, key heads, head
+    size, feed-forward size and vocabulary; every third layer a latent-attention layer (latent of four head sizes, half
+    a head size of rotated coordinates, a window of `window` tokens), the others attention layers; no loop."""
+    d, i, v, hq, hkv, hd = sizes(raw)
+    att = {"type": "attention", "mixer": {"heads": hq, "kv_heads": hkv, "dim": hd, "vdim": hd, "scale": hd ** -0.5,
+                                          "q_temp": {"coef": 0.1, "every": 1024}}, "mlp": {"kind": "dense", "ff": i, "limit": 7.0}}
+    lat = {"type": "latent_attention", "mixer": {"heads": hq, "dim": hd, "rot_dim": hd // 2, "vdim": hd, "kv_rank": 4 * hd,
+                                                 "scale": (hd + hd // 2) ** -0.5, "rot": {"base": 10000.0, "dims": hd // 2},
+                                                 "mask": {"size": window}}, "mlp": {"kind": "dense", "ff": i, "limit": 7.0}}
+    return {"architecture": "Venarax", "vocab": v, "width": d, "norm": {"eps": 1e-6},
+            "layers": [lat if n % 3 == 2 else att for n in range(layers)]}
+
+
+def time_venarax_kernels(torch, ops, raw, pk):
+    """The new design's kernels alone, each beside the like kernel of the dense decoder at equal sizes (inputs larger
+    than the L2; a CUDA graph of a few launches between events)."""
+    d, inter, _, hq, hkv, hd = sizes(raw)
+    dev, bf = "cuda:0", torch.bfloat16
+    g = torch.Generator(device=dev).manual_seed(0)
+    rnd = lambda *shape, dt=torch.float32: torch.randn(*shape, device=dev, generator=g).to(dt)
+
+    def us(fn, reps=5):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for _ in range(reps):
+                fn()
+        graph.replay()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        graph.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / reps * 1000
+
+    out = {}
+
+    def entry(name, t_new, t_like, nbytes=None, flops=None, like_bytes=None, like_flops=None, like=""):
+        e = {"us": round(t_new, 1), "like": like, "like_us": round(t_like, 1)}
+        if nbytes:
+            e["hbm_frac"] = round(nbytes / t_new / 1e3 / pk["hbm_gbs"], 3)
+            e["like_hbm_frac"] = round((like_bytes or nbytes) / t_like / 1e3 / pk["hbm_gbs"], 3)
+        if flops:
+            e["tensor_frac"] = round(flops / t_new / 1e6 / pk["bf16_tflops"], 4)
+            e["like_tensor_frac"] = round((like_flops or flops) / t_like / 1e6 / pk["bf16_tflops"], 4)
+        out[name] = e
+
+    # norms: 32,768 rows (the stream alone is past the L2)
+    rows = 32768
+    res, dl = rnd(rows, d), rnd(rows, d)
+    w = [rnd(d) for _ in range(4)]
+    o1, o2 = torch.empty(rows, d, dtype=bf, device=dev), torch.empty(rows, d, dtype=bf, device=dev)
+    t_new = us(lambda: ops.add_layernorm(res, dl, None, w[0], w[1], o1, 1e-6, None, w[2], w[3], o2))
+    t_like = us(lambda: (ops.add_rmsnorm(res, dl, w[0], o1, 1e-6), ops.add_rmsnorm(res, None, w[2], o2, 1e-6)))
+    entry("add_layernorm_two_outputs", t_new, t_like, rows * d * (4 + 4 + 4 + 2 + 2), like_bytes=rows * d * (4 + 4 + 4 + 2 + 4 + 2),
+          like="add_rmsnorm twice (the two norms of a layer)")
+    del res, dl, o1, o2
+    # gating: 16,384 rows of the feed-forward's width
+    rows = 16384
+    gu32, gu16 = rnd(rows, 2 * inter), rnd(rows, 2 * inter, dt=bf)
+    h = torch.empty(rows, inter, dtype=bf, device=dev)
+    t_new = us(lambda: ops.glu_clamped(gu32, h, 7.0, 1.702, 1.0))
+    t_like = us(lambda: ops.silu_mul(gu16, h))
+    entry("glu_clamped", t_new, t_like, rows * inter * (8 + 2), like_bytes=rows * inter * (4 + 2), like="silu_mul (bfloat16 in)")
+    del gu32, gu16, h
+    # attention: decoding rows (64 rows at 4,096 keys: the cache alone is past the L2) and one prompt of 4,096 tokens
+    page, ctx, b = PAGE, 4096, 64
+    pages = b * ctx // page
+    table = torch.arange(pages, dtype=torch.int32, device=dev).view(b, -1).contiguous()
+    sinks = rnd(hq)
+    for name, dk, dv, vw, h_kv, window in (("sink_attention", hd, hd, hd, hkv, None), ("latent_attention", 4 * hd + hd // 2, 4 * hd, 0, 1, 1024)):
+        kp = rnd(pages, h_kv, page, dk, dt=bf)
+        vp = kp if not vw else rnd(pages, h_kv, page, dv, dt=bf)
+        q = rnd(b, hq * dk)
+        o = torch.empty(b, hq * dv, dtype=bf, device=dev)
+        pos = torch.full((b,), ctx - 1, dtype=torch.int32, device=dev)
+        slot = torch.arange(b, dtype=torch.int32, device=dev)
+        sk = sinks if vw else None
+        seen = min(ctx, window or ctx)
+        t_new = us(lambda: ops.attention_wide(q, kp, vp, o, sk, pos, slot, table, hq, h_kv, dk, dv, window, 0.1))
+        nbytes = b * seen * h_kv * (dk + (dv if vw else 0)) * 2
+        if vw:  # the dense decoder's exact kernel and its fast decode kernel at the same sizes
+            q16, o16 = q.to(bf), torch.empty(b, hq * hd, dtype=bf, device=dev)
+            t_like = us(lambda: ops.attention_generic(q16, kp, vp, o16, pos, slot, table, hq, hkv, hd, None, 0.1))
+            entry(name + "_decode", t_new, t_like, nbytes, like="attention_generic (the exact kernel)")
+            if ops.attention_decode_supports(hd, hq // hkv):
+                t_fast = us(lambda: ops.attention_decode_cluster(q16, kp, vp, o16, pos, slot, table, hq, hkv, hd, None, 0.1, 4,
+                                                                 min(2, ops.attention_decode_cluster_max_stages(hd))))
+                out[name + "_decode"].update(fast_us=round(t_fast, 1), fast_hbm_frac=round(nbytes / t_fast / 1e3 / pk["hbm_gbs"], 3),
+                                             fast="attention_decode_cluster (mma.sync, bfloat16)")
+        else:
+            entry(name + "_decode", t_new, t_new, nbytes, like="(no like kernel: one plane read for keys and values)")
+        # one prompt of 4,096 tokens in one step
+        n = ctx
+        posp = torch.arange(n, dtype=torch.int32, device=dev)
+        slotp = torch.zeros(n, dtype=torch.int32, device=dev)
+        qp, op = rnd(n, hq * dk), torch.empty(n, hq * dv, dtype=bf, device=dev)
+        t_new = us(lambda: ops.attention_wide(qp, kp, vp, op, sk, posp, slotp, table, hq, h_kv, dk, dv, window, 0.1, share_rows=True), reps=2)
+        pairs = n * (n + 1) // 2 if not window else sum(min(p + 1, window) for p in range(n))
+        flops = 2 * pairs * hq * (dk + dv)
+        if vw:
+            qp16, op16 = qp.to(bf), torch.empty(n, hq * hd, dtype=bf, device=dev)
+            t_like = us(lambda: ops.attention_generic(qp16, kp, vp, op16, posp, slotp, table, hq, hkv, hd, None, 0.1, share_rows=True), reps=2)
+            entry(name + "_prefill", t_new, t_like, flops=flops, like="attention_generic (the exact kernel)")
+            if ops.attention_prefill_tc_supports(hd, page):
+                t0 = torch.arange(0, n, 128, dtype=torch.int32, device=dev)
+                tn = torch.full_like(t0, 128)
+                tiles = t0.numel()
+                splits, alone, run_tiles = ops.attention_prefill_tc_plan(tiles, hq, hkv, hd, n, tiles * (tiles + 1) // 2)
+                words = ops.attention_prefill_tc_scratch_words(tiles, hq, hd, splits)
+                scratch = torch.zeros(max(words, 1), dtype=torch.float32, device=dev) if words else None
+                counters = torch.zeros(tiles * hq, dtype=torch.int32, device=dev) if words else None
+                t_fast = us(lambda: ops.attention_prefill_tc(qp16, kp, vp, op16, t0, tn, tiles, posp, slotp, table, hq, hkv, hd, None, 0.1,
+                                                             splits, scratch, counters, alone=alone, run_tiles=run_tiles), reps=2)
+                out[name + "_prefill"].update(fast_us=round(t_fast, 1), fast_tensor_frac=round(flops / t_fast / 1e6 / pk["bf16_tflops"], 4),
+                                              fast="attention_prefill_tc (tcgen05)")
+        else:
+            entry(name + "_prefill", t_new, t_new, flops=flops, like="(no like kernel)")
+        del kp, vp, q, o, qp, op
+    # between the input product and the attention: 16,384 rows
+    rows = 16384
+    pos = (torch.arange(rows, dtype=torch.int32, device=dev) % 4096).contiguous()
+    slot = (torch.arange(rows, dtype=torch.int32, device=dev) // 4096).contiguous()
+    pages = rows // page
+    table = torch.arange(pages, dtype=torch.int32, device=dev).view(4, -1).contiguous()
+    qkvw = (hq + 2 * hkv) * hd
+    proj = rnd(rows, qkvw)
+    kp, vp = torch.zeros(pages, hkv, page, hd, dtype=bf, device=dev), torch.zeros(pages, hkv, page, hd, dtype=bf, device=dev)
+    qo = torch.empty(rows, hq * hd, device=dev)
+    t_new = us(lambda: ops.qk_norm_store(proj, w[0].new_ones(hq * hd), w[0].new_ones(hkv * hd), 1e-6, 0.1, 1024, pos, slot, table, qo, kp, vp, hkv, hd, hd))
+    proj16, qo16 = proj.to(bf), torch.empty(rows, hq * hd, dtype=bf, device=dev)
+    ang = torch.zeros(4096, hd // 2, 2, device=dev)
+    t_like = us(lambda: ops.rope_kv_store(proj16, None, pos, slot, table, ang, hd, False, qo16, kp, vp, hq, hkv, hd))
+    entry("qk_norm_store", t_new, t_like, rows * (qkvw * 4 + hq * hd * 4 + 2 * hkv * hd * 2), like_bytes=rows * (qkvw * 2 + hq * hd * 2 + 2 * hkv * hd * 2),
+          like="rope_kv_store (bfloat16 in and out)")
+    return out
+
+
+def workload_venarax(a, pk):
+    """The Venarax design at the layer sizes of the Qwen2.5 shapes, beside the dense decoder at the same sizes: decode
+    at the headline batch and context, one prompt of `--prefill` tokens, and the new kernels alone."""
+    import torch
+
+    from machserve_b200 import ops
+
+    out = {}
+    for shape in ("qwen2.5-0.5b", "qwen2.5-1.5b", "qwen2.5-7b"):
+        raw = SHAPES[shape]
+        layers = min(raw["num_hidden_layers"], a.layers or 12)  # (layers of equal sizes: twelve tell what all tell)
+        res = {"layers": layers}
+        steps = max(10, a.steps // 2)
+        for which in ("venarax", "dense"):
+            kw = dict(config=venarax_config(raw, layers), vocab=raw["vocab_size"]) if which == "venarax" else {}
+            b = DecodeBench(a, raw, layers, "bf16", a.batch, a.context + 4 * (steps + a.warmup) + a.batch + 64, **kw)
+            times, launches = b.time_decode(a.batch, a.context, steps, a.warmup, blocks=3, sampled=False)
+            pms = b.time_prefill(a.prefill, 2, reps=3)
+            res[which] = {"decode_ms_per_step": round(times[len(times) // 2], 4), "decode_tokens_per_s": round(a.batch * 1000.0 / times[len(times) // 2], 1),
+                          "launches_per_step": launches // steps, "prefill_ms": round(pms, 3), "prefill_tokens_per_s": round(a.prefill * 1000.0 / pms, 1)}
+            b.runner.check_device_status()
+            b.release_all()
+            del b
+            free_device_memory()
+        res["kernels"] = time_venarax_kernels(torch, ops, raw, pk)
+        free_device_memory()
+        out[shape] = res
+    return {"batch": a.batch, "context": a.context, "prefill_tokens": a.prefill, "dtype": "bf16",
+            "data": "random-init weights drawn on the device, seeded uniform random token ids", "peaks": pk["source"], "sizes": out}
 
 
 def workload_serving(a, pk):
@@ -638,7 +818,8 @@ def main() -> int:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--dtype", default="bf16", choices=["bf16", "bfloat16", "f32", "fp32", "float32"])
     ap.add_argument("--only", default="headline,fp32,serving_1p5b,mixed_7b",
-                    help="which parts to run: headline, fp32, serving_1p5b, mixed_7b (comma separated)")
+                    help="which parts to run: headline, fp32, serving_1p5b, mixed_7b (comma separated); venarax, which is not "
+                         "among the defaults, times the Venarax design beside the dense decoder at equal layer sizes")
     ap.add_argument("--no-points", action="store_true", help="skip the further batch sizes and the prefill")
     ap.add_argument("--profile", default=None, choices=["decode", "prefill", "mixed"],
                     help="which timed region is bracketed by cudaProfilerStart/Stop (for ncu --profile-from-start off)")
@@ -741,6 +922,8 @@ def main() -> int:
         line["serving_1p5b"] = workload_serving(a, pk)
     if "mixed_7b" in only:
         line["mixed_7b"] = workload_mixed(a, pk)
+    if "venarax" in only:
+        line["venarax"] = workload_venarax(a, pk)
     print(json.dumps(line))
     return 0
 

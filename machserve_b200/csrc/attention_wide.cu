@@ -228,35 +228,55 @@ attention_wide_kernel(const float* __restrict__ q, const TC* __restrict__ k_page
   }
 }
 
+template <typename TC, int W, int NACC, int R, bool HEADS>
+static int launch_attention_wide_form(const float* q, const void* k_pages, const void* v_pages, void* out, const float* sinks,
+                                      const int* positions, const int* slots, const int* block_table, int max_pages, int num_pages,
+                                      int tokens, int hq, int hkv, int dk, int dv, int vw, int page_size, int window, float scale,
+                                      cudaStream_t stream) {
+  const int groups = hq / hkv;
+  const size_t smem = ((size_t)R * dk + (size_t)W * 32 * (AW_KC + 1) + (size_t)W * R * (dv + 2)) * sizeof(float);
+  MS_REQUIRE(smem <= 200 * 1024, "attention_wide: keys of %d coordinates need %zu bytes of shared memory", dk, smem);
+  const unsigned blocks = HEADS ? (unsigned)tokens * (unsigned)hkv * (unsigned)((groups + R - 1) / R)
+                                : (unsigned)((tokens + R - 1) / R) * (unsigned)hq;
+  auto kern = attention_wide_kernel<TC, W, NACC, R, HEADS>;
+  static size_t configured = 0;
+  if (smem > configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    MS_REQUIRE(e == cudaSuccess, "attention_wide: cannot get shared memory: %s", cudaGetErrorString(e));
+    configured = smem;
+  }
+  kern<<<blocks, W * 32, smem, stream>>>(q, (const TC*)k_pages, (const TC*)v_pages, (TC*)out, sinks, positions, slots, block_table,
+                                         max_pages, num_pages, tokens, hq, hkv, dk, dv, vw, page_size, window, scale);
+  MS_LAUNCH_CHECK("attention_wide");
+  return 0;
+}
+
+// Rows of portions: R consecutive rows a block.  Rows alone in their sequences: the heads of a group share a block, R of
+// them, or, when that would leave most SMs without a block (few rows, few key heads), every head gets a block of its
+// own: a row's arithmetic is the same in every form, so the choice changes no bit of the result.
 template <typename TC, int W, int NACC, int R>
 static int launch_attention_wide(const float* q, const void* k_pages, const void* v_pages, void* out, const float* sinks,
                                  const int* positions, const int* slots, const int* block_table, int max_pages, int num_pages,
                                  int tokens, int hq, int hkv, int dk, int dv, int vw, int page_size, int window, float scale,
                                  bool heads, cudaStream_t stream) {
+#define MS_AW_ARGS q, k_pages, v_pages, out, sinks, positions, slots, block_table, max_pages, num_pages, tokens, hq, hkv, dk, dv, vw, \
+                   page_size, window, scale, stream
+  if (!heads) return launch_attention_wide_form<TC, W, NACC, R, false>(MS_AW_ARGS);
   const int groups = hq / hkv;
-  const size_t smem = ((size_t)R * dk + (size_t)W * 32 * (AW_KC + 1) + (size_t)W * R * (dv + 2)) * sizeof(float);
-  MS_REQUIRE(smem <= 200 * 1024, "attention_wide: keys of %d coordinates need %zu bytes of shared memory", dk, smem);
-  const unsigned blocks = heads ? (unsigned)tokens * (unsigned)hkv * (unsigned)((groups + R - 1) / R)
-                                : (unsigned)((tokens + R - 1) / R) * (unsigned)hq;
-#define MS_AW_GO(H)                                                                                                       \
-  do {                                                                                                                    \
-    auto kern = attention_wide_kernel<TC, W, NACC, R, H>;                                                                 \
-    static size_t configured = 0;                                                                                         \
-    if (smem > configured) {                                                                                              \
-      cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);                 \
-      MS_REQUIRE(e == cudaSuccess, "attention_wide: cannot get shared memory: %s", cudaGetErrorString(e));                \
-      configured = smem;                                                                                                  \
-    }                                                                                                                     \
-    kern<<<blocks, W * 32, smem, stream>>>(q, (const TC*)k_pages, (const TC*)v_pages, (TC*)out, sinks, positions, slots,  \
-                                           block_table, max_pages, num_pages, tokens, hq, hkv, dk, dv, vw, page_size, window, scale); \
-  } while (0)
-  if (heads)
-    MS_AW_GO(true);
-  else
-    MS_AW_GO(false);
-#undef MS_AW_GO
-  MS_LAUNCH_CHECK("attention_wide");
-  return 0;
+  int sms = 148;
+  {
+    static int cached = 0;
+    if (!cached) {
+      int dev = 0;
+      if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&cached, cudaDevAttrMultiProcessorCount, dev);
+      if (cached <= 0) cached = 148;
+    }
+    sms = cached;
+  }
+  if (groups > 1 && (long long)tokens * hkv * ((groups + R - 1) / R) < 2LL * sms)
+    return launch_attention_wide_form<TC, W, NACC, 1, true>(MS_AW_ARGS);
+  return launch_attention_wide_form<TC, W, NACC, R, true>(MS_AW_ARGS);
+#undef MS_AW_ARGS
 }
 
 // q [tokens, hq*dk] float32; out [tokens, hq*dv] in the cache's type.  window <= 0: every earlier key is visible.

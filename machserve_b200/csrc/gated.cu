@@ -22,10 +22,52 @@ __global__ void glu_clamped_kernel(const float* __restrict__ gate_up, T* __restr
   out[i] = ms_from_float<T>(g / (1.f + expf(-alpha * g)) * (u + shift));
 }
 
+// Eight columns per thread with 16- and 32-byte accesses, for widths that are a multiple of 8.
+template <typename T>
+__global__ void glu_clamped_vec_kernel(const float* __restrict__ gate_up, T* __restrict__ out, int inter, float limit, float alpha,
+                                       float shift) {
+  ms_pdl_trigger();
+  ms_pdl_wait();
+  const int row = blockIdx.y;
+  const int c = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
+  if (c >= inter) return;
+  const float* gp = gate_up + (size_t)row * 2 * inter + c;
+  const float4 g0 = *reinterpret_cast<const float4*>(gp), g1 = *reinterpret_cast<const float4*>(gp + 4);
+  const float4 u0 = *reinterpret_cast<const float4*>(gp + inter), u1 = *reinterpret_cast<const float4*>(gp + inter + 4);
+  const float g[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w}, u[8] = {u0.x, u0.y, u0.z, u0.w, u1.x, u1.y, u1.z, u1.w};
+  float r[8];
+#pragma unroll
+  for (int k = 0; k < 8; ++k) {
+    const float gk = fminf(g[k], limit), uk = fminf(fmaxf(u[k], -limit), limit);
+    r[k] = gk / (1.f + expf(-alpha * gk)) * (uk + shift);
+  }
+  T* o = out + (size_t)row * inter + c;
+  if constexpr (sizeof(T) == 2) {
+    uint4 pk;
+    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&pk);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) h[k] = __floats2bfloat162_rn(r[2 * k], r[2 * k + 1]);
+    *reinterpret_cast<uint4*>(o) = pk;
+  } else {
+    *reinterpret_cast<float4*>(o) = make_float4(r[0], r[1], r[2], r[3]);
+    *reinterpret_cast<float4*>(o + 4) = make_float4(r[4], r[5], r[6], r[7]);
+  }
+}
+
 MS_API int ms_glu_clamped(const float* gate_up, void* out, int dtype, int rows, int inter, float limit, float alpha, float shift,
                           cudaStream_t stream) {
   if (rows == 0) return 0;
   MS_REQUIRE(rows > 0 && inter > 0 && limit > 0.f, "glu_clamped: bad arguments rows=%d inter=%d limit=%g", rows, inter, limit);
+  if (inter % 8 == 0 && rows <= 65535 && ((uintptr_t)gate_up | (uintptr_t)out) % 16 == 0 && (dtype == MS_F32 || dtype == MS_BF16)) {
+    dim3 grid((inter / 8 + 127) / 128, rows);
+    if (dtype == MS_F32)
+      MS_LAUNCH_RESULT("glu_clamped", ms_launch(glu_clamped_vec_kernel<float>, grid, dim3(128), 0, stream, 1, true, gate_up, (float*)out,
+                                                inter, limit, alpha, shift));
+    else
+      MS_LAUNCH_RESULT("glu_clamped", ms_launch(glu_clamped_vec_kernel<__nv_bfloat16>, grid, dim3(128), 0, stream, 1, true, gate_up,
+                                                (__nv_bfloat16*)out, inter, limit, alpha, shift));
+    return 0;
+  }
   const size_t total = (size_t)rows * inter;
   const unsigned blocks = (unsigned)((total + 255) / 256);
   if (dtype == MS_F32)

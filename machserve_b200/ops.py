@@ -76,6 +76,7 @@ class _Signatures:
     ms_qk_norm_store = [P, I, P, P, F, F, I, P, P, P, I, I, I, P, P, P, I, I, I, I, I, I, I, P]
     ms_latent_encode = [P, I, I, P, F, P, I, I, P, P, P, I, I, I, P, P, I, P, I, I, I, I, I, I, I, P]
     ms_attention_wide = [P, P, P, P, I, P, P, P, P, I, I, I, I, I, I, I, I, I, I, F, I, P]
+    ms_attention_wide_mma = [P, P, P, P, P, P, P, P, I, I, P, P, I, I, I, I, I, I, I, I, I, F, I, P, P]
     ms_rope_kv_store = [P, I, I, P, P, P, P, I, I, P, I, I, P, P, P, I, I, I, I, I, I, P]
     ms_attention_generic = [P, P, P, P, I, I, P, P, P, I, I, I, I, I, I, I, I, F, I, P]
     ms_gemm_f32 = [P, I, P, P, P, I, I, I, I, P]
@@ -1001,6 +1002,50 @@ def attention_wide(q, k_pages, v_pages, out, sinks, positions, slot_of_token, bl
         _ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(out), _code(k_pages), _ptr(sinks), _ptr(positions), _ptr(slot_of_token),
         _ptr(block_table), block_table.shape[1], k_pages.shape[0], tokens, num_heads, num_kv_heads, dk, dv, v_pages.shape[3],
         k_pages.shape[2], int(window or 0), float(scale), int(share_rows), _stream()), "attention_wide")
+    return out
+
+
+def attention_wide_mma_supports(dk: int, dv: int, vw: int, separate_v: bool) -> bool:
+    """Whether the tensor-core form covers the widths (dk in steps of 16, dv and the value rows in steps of 8, dv <= 512,
+    and a key tile that fits the shared memory)."""
+    return bool(lib().ms_attention_wide_mma_supports(int(dk), int(dv), int(vw), int(separate_v)))
+
+
+def attention_wide_mma_scratch_words(items: int, dv: int, splits: int) -> int:
+    """float32 words of scratch for `items` (decoding rows x key heads x chunks of 16 heads) cut into `splits` runs of keys."""
+    fn = lib().ms_attention_wide_mma_scratch_words
+    fn.restype = c_longlong
+    fn.argtypes = [c_int, c_int, c_int]
+    return int(fn(int(items), int(dv), int(splits)))
+
+
+def attention_wide_mma(q, k_pages, v_pages, out, sinks, positions, slot_of_token, block_table, unit_row0, unit_rows, units: int,
+                       heads: bool, num_heads: int, num_kv_heads: int, dk: int, dv: int, window: Optional[int], scale: float,
+                       splits: int = 1, scratch: Optional[torch.Tensor] = None):
+    """attention_wide on the tensor cores (mma.sync, bfloat16 cache and output, float32 queries and softmax).
+    heads False: `units` tiles of at most 16 consecutive rows of one sequence, tile u = rows unit_row0[u] .. + unit_rows[u].
+    heads True: `units` rows that are alone in their sequences (unit_row0[u], or u without a list; -1 for none); the query
+    heads that share a key head fill the tensor core's rows, and a row's key tiles are cut into `splits` runs that meet in
+    `scratch` (float32, attention_wide_mma_scratch_words).  v_pages may be k_pages itself (a latent cache)."""
+    _need(q.dtype == torch.float32 and q.is_contiguous() and out.is_contiguous() and out.dtype == torch.bfloat16
+          and k_pages.dtype == torch.bfloat16 and v_pages.dtype == torch.bfloat16, "attention_wide_mma: bad dtypes or layout")
+    _need(k_pages.is_contiguous() and v_pages.is_contiguous() and tuple(k_pages.shape[1:]) == (num_kv_heads, k_pages.shape[2], dk)
+          and tuple(v_pages.shape[:3]) == tuple(k_pages.shape[:3]) and v_pages.shape[3] >= dv, "attention_wide_mma: bad page shapes")
+    _need(sinks is None or (sinks.dtype == torch.float32 and sinks.numel() == num_heads), "attention_wide_mma: bad sinks")
+    _need(block_table.dtype == torch.int32 and block_table.is_contiguous(), "attention_wide_mma: bad block table")
+    for lst in (unit_row0, unit_rows):
+        _need(lst is None or (lst.dtype == torch.int32 and lst.numel() >= units), "attention_wide_mma: bad unit lists")
+    if splits > 1:
+        groups = num_heads // num_kv_heads
+        need = attention_wide_mma_scratch_words(units * num_kv_heads * (-(-groups // 16)), dv, splits)
+        _need(scratch is not None and scratch.dtype == torch.float32 and scratch.numel() >= need, "attention_wide_mma: scratch too small")
+    _check(lib().ms_attention_wide_mma(
+        _ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(out), _ptr(sinks), _ptr(positions), _ptr(slot_of_token), _ptr(block_table),
+        block_table.shape[1], k_pages.shape[0], _ptr(unit_row0), _ptr(unit_rows), int(units), int(heads), num_heads, num_kv_heads,
+        dk, dv, v_pages.shape[3], k_pages.shape[2], int(window or 0), float(scale), int(splits), _ptr(scratch), _stream()),
+        "attention_wide_mma")
+    if splits > 1:
+        count_launches(1)  # the merge of the splits
     return out
 
 

@@ -5,12 +5,13 @@ from __future__ import annotations
 import torch
 
 from .. import ops
+from . import wide_attend
 from ..weights.loader import TensorDecl
 from .base import POSITION_ENCODINGS, CachePlane, Mixer, PagedCache, matrix, register_mixer, vector_f32
 
 
 @register_mixer("latent_attention")
-class LatentAttention(Mixer):
+class LatentAttention(wide_attend.WideAttendPlan, Mixer):
     """x -> q = Wq x, head by head [dn unrotated | dr rotated];  Wdkv x = [latent (r) | key part (dr)].
     c = latent / rms(latent) * w (eps inside the root); kr = the key part, rotated, shared by all heads.
     Per head h: k_h = Wuk_h c (dn), v_h = Wuv_h c (dv); score = scale * (q_plain . k_h + q_rot . kr) over the keys the
@@ -70,6 +71,7 @@ class LatentAttention(Mixer):
         self.w_uv = matrix(tensors[p + "uv"].reshape(self.heads, self.dv, self.r), rt)
         self.w_o = matrix(tensors[p + "o"], rt)
         self.latent_norm = vector_f32(tensors[p + "dkv.norm"])
+        self.fast = wide_attend.supports(rt, self.kvw, self.r, self.kvw, False)  # bfloat16: the tensor-core kernel
         self.table, self.rot = None, 0
         if self.position is not None:
             self.position.bind(tensors, rt)
@@ -92,8 +94,8 @@ class LatentAttention(Mixer):
                           q_wide, q_plain, pages, h, self.dn, self.dr, r, store=owns_cache)
         ops.linear_heads(q_plain, self.w_uk_t, q_wide[:, :, :r])
         attended = ws.get("latent_attn.attended", (t, h, r), rt.dtype)
-        ops.attention_wide(q_wide.view(t, h * wide), pages, pages, attended.view(t, h * r), None, ctx.positions, ctx.slot_of_token,
-                           table, h, 1, wide, r, self.window, self.scale, share_rows=ctx.max_query_len > 1)
+        wide_attend.attend(ctx, rt, self.fast, table, q_wide.view(t, h * wide), pages, pages, attended.view(t, h * r), None, h, 1, wide, r,
+                           self.window, self.scale)
         values = ws.get("latent_attn.values", (t, h, self.dv), torch.float32)
         ops.linear_heads(attended, self.w_uv, values)
         if self.has_gate:

@@ -5,12 +5,13 @@ from __future__ import annotations
 import torch
 
 from .. import ops
+from . import wide_attend
 from ..weights.loader import TensorDecl
 from .base import CachePlane, Mixer, PagedCache, matrix, register_mixer, vector_f32
 
 
 @register_mixer("sink_attention")
-class SinkAttention(Mixer):
+class SinkAttention(wide_attend.WideAttendPlan, Mixer):
     """q = Wq x, k = Wk x, v = Wv x (no biases, one product).  The whole q row and the whole k row are each divided by
     their root mean square (eps inside the root) and multiplied by a weight of their own, before they are split into
     heads.  The query at position p is then multiplied by 1 + coef * ln(floor((p + 1) / every) + 1).  Positions enter
@@ -18,7 +19,8 @@ class SinkAttention(Mixer):
     0..p (or the last `window`); the softmax's denominator also holds exp(sink_h), a learned number per head that has no
     value and is not scaled.  Keys have `key_dim` and values `value_dim` coordinates per head; the output projection
     reads the heads' values side by side.  Norms, temperature, scores and softmax are float32; the query stays float32
-    up to the scores; the delta is float32.
+    up to the scores (the exact kernel) or is rounded to bfloat16 as it enters the tensor core (bfloat16 runtime, widths
+    the tensor-core kernel covers); the delta is float32.
 
     params: prefix, hidden_size, num_heads, num_kv_heads, key_dim, value_dim, scale, eps, temp_coef (0: none),
     temp_every, window (or None), sink (False: a plain softmax).  Tensors under the prefix: q, k, v, o (matrices),
@@ -64,6 +66,7 @@ class SinkAttention(Mixer):
         self.w_o = matrix(tensors[p + "o"], rt)
         self.q_norm, self.k_norm = vector_f32(tensors[p + "q.norm"]), vector_f32(tensors[p + "k.norm"])
         self.sinks = vector_f32(tensors[p + "sink"]) if self.has_sink else None
+        self.fast = wide_attend.supports(rt, self.dk, self.dv, self.dv, True)  # bfloat16: the tensor-core kernel
 
     def forward(self, ctx, x, cache, owns_cache=True):
         rt, t = self.rt, x.shape[0]
@@ -77,7 +80,7 @@ class SinkAttention(Mixer):
         ops.qk_norm_store(proj, self.q_norm, self.k_norm, self.eps, self.coef, self.every, ctx.positions, ctx.slot_of_token, table,
                           q, k_pages, v_pages, self.hkv, self.dk, self.dv, store=owns_cache)
         out = ws.get("sink_attn.out", (t, self.hq * self.dv), rt.dtype)
-        ops.attention_wide(q, k_pages, v_pages, out, self.sinks, ctx.positions, ctx.slot_of_token, table, self.hq, self.hkv,
-                           self.dk, self.dv, self.window, self.scale, share_rows=ctx.max_query_len > 1)
+        wide_attend.attend(ctx, rt, self.fast, table, q, k_pages, v_pages, out, self.sinks, self.hq, self.hkv, self.dk, self.dv,
+                           self.window, self.scale)
         delta = ws.get("mixer.delta_f32", (t, self.hidden), torch.float32)
         return ops.linear(out, self.w_o, None, delta)

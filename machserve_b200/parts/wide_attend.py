@@ -1,0 +1,88 @@
+"""What the mixers with wide or unequal key and value rows share: the work lists of their tensor-core attention kernel,
+and the choice between it and the exact kernel."""
+from __future__ import annotations
+
+import torch
+
+from .. import ops
+from .base import WorkPlan
+
+PLAN = "row_tiles16"  # the key of the work lists: every such mixer of a model shares them
+TILE = 16             # rows of a portion that one block of the tensor-core kernel attends
+CONTEXT_BUCKET = 512  # a decoding row's run of keys is chosen from the longest context rounded up to this
+
+
+def plan_words(max_rows: int, max_seqs: int) -> int:
+    return 4 * max_seqs + 16 + 2 * (max_rows // TILE + max_seqs + 8)
+
+
+def plan(step) -> WorkPlan:
+    """Rows that are alone in their sequence (decoding) go to the form whose 16 rows are the query heads of a token;
+    portions of prompts are cut into tiles of up to 16 consecutive rows."""
+    single, t0, tn = [], [], []
+    longest = 0
+    for row, n, start in zip(step.row0, step.count, step.start):
+        if n == 0:
+            continue
+        if n == 1:
+            single.append(row)
+            longest = max(longest, start + 1)
+        else:
+            for a in range(0, n, TILE):
+                t0.append(row + a)
+                tn.append(min(TILE, n - a))
+    cls = -(-longest // CONTEXT_BUCKET)
+    if step.bucketed:  # lists of a few lengths (an entry of no rows does nothing), the context class a power of two
+        pad = -len(t0) % 8
+        t0 += [0] * pad
+        tn += [0] * pad
+        if single:
+            want = 16
+            while want < len(single):
+                want *= 4
+            single += [-1] * (want - len(single))
+        cls = 1 << (cls - 1).bit_length() if cls > 0 else 0
+    return WorkPlan({"single_rows": single, "tile_row0": t0, "tile_rows": tn}, (cls,))
+
+
+def supports(rt, dk: int, dv: int, vw: int, separate_v: bool) -> bool:
+    return rt.dtype == torch.bfloat16 and ops.attention_wide_mma_supports(dk, dv, vw, separate_v)
+
+
+def attend(ctx, rt, fast: bool, table, q, k_pages, v_pages, out, sinks, hq: int, hkv: int, dk: int, dv: int, window, scale: float):
+    """Every row of q over its sequence's pages: on the tensor cores when the widths allow it in bfloat16 (decoding rows
+    with their key tiles cut into as many runs as fill the GPU, portions in tiles of 16 rows), else the exact kernel."""
+    if not fast:
+        return ops.attention_wide(q, k_pages, v_pages, out, sinks, ctx.positions, ctx.slot_of_token, table, hq, hkv,
+                                  dk, dv, window, scale, share_rows=ctx.max_query_len > 1)
+    work = ctx.work[PLAN]
+    singles, tiles = work.sizes["single_rows"], work.sizes["tile_row0"]
+    if singles:
+        items = singles * hkv * (-(-(hq // hkv) // 16))
+        keys = work.shape[0] * CONTEXT_BUCKET
+        if window:
+            keys = min(keys, window + 63)
+        splits = max(1, min(2 * rt.sm_count // items, -(-keys // 64), 32))
+        scratch = None
+        if splits > 1:
+            scratch = rt.workspace.get("wide_attend.splits", (ops.attention_wide_mma_scratch_words(items, dv, splits),), torch.float32)
+        rows = None if tiles == 0 and singles == q.shape[0] else work.lists["single_rows"]
+        ops.attention_wide_mma(q, k_pages, v_pages, out, sinks, ctx.positions, ctx.slot_of_token, table, rows, None, singles, True,
+                               hq, hkv, dk, dv, window, scale, splits, scratch)
+    if tiles:
+        ops.attention_wide_mma(q, k_pages, v_pages, out, sinks, ctx.positions, ctx.slot_of_token, table, work.lists["tile_row0"],
+                               work.lists["tile_rows"], tiles, False, hq, hkv, dk, dv, window, scale)
+    return out
+
+
+class WideAttendPlan:
+    """Mixin of the mixers that attend through `attend`: their shared work lists."""
+
+    def plan_key(self):
+        return PLAN
+
+    def plan(self, step):
+        return plan(step)
+
+    def plan_words(self, max_rows, max_seqs):
+        return plan_words(max_rows, max_seqs)

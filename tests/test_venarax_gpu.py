@@ -161,6 +161,65 @@ def test_attention_with_sink_and_unequal_widths(dk, dv, hq, hkv, window, sink, p
     assert_close(outs[0].reshape(len(rows), -1), want.reshape(len(rows), -1), 2e-5 if dtype == "float32" else 1e-2, "attention")
 
 
+@pytest.mark.parametrize("dk,dv,hq,hkv,window,sink,latent,page", [
+    (64, 64, 4, 2, None, True, False, 16), (96, 96, 6, 2, None, True, False, 8), (48, 80, 3, 1, 21, True, False, 16),
+    (160, 128, 4, 1, 33, False, True, 16), (288, 256, 14, 1, 50, False, True, 16), (576, 512, 2, 1, 40, False, True, 8),
+    (32, 24, 20, 1, None, True, False, 8),
+])
+def test_tensor_core_attention_with_sink_and_unequal_widths(dk, dv, hq, hkv, window, sink, latent, page):
+    """The bfloat16 tensor-core form: tiles of rows of two sequences, decoding rows whose keys are cut into runs that
+    are merged, values inside the keys' own plane (a latent cache), against the plain softmax and the exact kernel."""
+    torch = _torch()
+    from machserve_b200 import ops
+
+    rng = np.random.default_rng(dk * 7 + dv)
+    bf = torch.bfloat16
+    lens = [150, 41]
+    kp, table = _paged(rng, lens, hkv, dk, page, "bfloat16")
+    ks = [rng.normal(size=(n, hkv, dk)).astype(np.float32) for n in lens]
+    for s in range(2):
+        _fill_pages(kp, table, s, ks[s], page)
+    kd = _dev(kp, bf)
+    if latent:
+        vd, vs = kd, [k[:, :, :dv] for k in ks]
+    else:
+        vp = np.zeros(kp.shape[:3] + (dv,), dtype=np.float32)
+        vs = [rng.normal(size=(n, hkv, dv)).astype(np.float32) for n in lens]
+        for s in range(2):
+            _fill_pages(vp, table, s, vs[s], page)
+        vd = _dev(vp, bf)
+    ks = [_dev(k, bf).float().cpu().numpy().astype(np.float64) for k in ks]
+    vs = [_dev(np.ascontiguousarray(v), bf).float().cpu().numpy().astype(np.float64) for v in vs]
+    assert ops.attention_wide_mma_supports(dk, dv, vd.shape[3], not latent)
+    sinks = rng.normal(size=hq).astype(np.float32) * 2 if sink else None
+    scale = 0.5 / np.sqrt(dk)
+    # rows 0..36: positions 100..136 of sequence 0 (tiles of 16, 16 and 5 rows); row 37: the last position of sequence 0,
+    # decoded; rows 38..40: the first three positions of sequence 1; row 41: position 40 of sequence 1, decoded
+    rows = [(0, p) for p in range(100, 137)] + [(0, 149)] + [(1, p) for p in range(3)] + [(1, 40)]
+    q = rng.normal(size=(len(rows), hq, dk)).astype(np.float32)
+    q_held = _dev(q, bf).float().cpu().numpy().astype(np.float64)  # the tensor core reads the queries as bfloat16
+    pos = torch.tensor([p for _, p in rows], dtype=torch.int32, device="cuda")
+    slot = torch.tensor([s for s, _ in rows], dtype=torch.int32, device="cuda")
+    ints = lambda v: torch.tensor(v, dtype=torch.int32, device="cuda")
+    want = np.zeros((len(rows), hq, dv))
+    for s in range(2):
+        idx = [i for i, (ss, _) in enumerate(rows) if ss == s]
+        want[idx] = _plain_attend(q_held[idx], ks[s], vs[s], [rows[i][1] for i in idx], window, scale, sinks, hq // hkv)
+    sk = None if sinks is None else _dev(sinks)
+    for splits in (1, 3):
+        out = torch.full((len(rows), hq * dv), 7.0, dtype=bf, device="cuda")
+        ops.attention_wide_mma(_dev(q).view(len(rows), hq * dk), kd, vd, out, sk, pos, slot, _dev(table), ints([0, 16, 32, 38, 0]),
+                               ints([16, 16, 5, 3, 0]), 5, False, hq, hkv, dk, dv, window, scale)
+        items = 3 * hkv * (-(-(hq // hkv) // 16))
+        scratch = torch.empty(max(1, ops.attention_wide_mma_scratch_words(items, dv, splits)), device="cuda")
+        ops.attention_wide_mma(_dev(q).view(len(rows), hq * dk), kd, vd, out, sk, pos, slot, _dev(table), ints([37, -1, 41]), None, 3, True,
+                               hq, hkv, dk, dv, window, scale, splits, scratch)
+        assert_close(out.float().cpu().numpy(), want.reshape(len(rows), -1), 1.5e-2, f"tensor-core attention, {splits} runs of keys")
+    exact = torch.zeros(len(rows), hq * dv, dtype=bf, device="cuda")
+    ops.attention_wide(_dev(q).view(len(rows), hq * dk), kd, vd, exact, sk, pos, slot, _dev(table), hq, hkv, dk, dv, window, scale, share_rows=True)
+    assert_close(out.float().cpu().numpy(), exact.float().cpu().numpy(), 2e-2, "tensor-core form against the exact kernel")
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_attention_one_key_stands_out(dtype):
     """One key among hundreds is made to carry nearly all the weight.  Far back, on a page border, just inside the

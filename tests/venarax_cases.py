@@ -81,6 +81,20 @@ CASES = {
         },
         seed=14, page=8,
     ),
+    # widths that the bfloat16 engine's tensor-core attention covers in every layer (key rows in steps of 16, value rows
+    # in steps of 8), a window that is no multiple of a tile of keys, more query heads per key head than a tile has rows
+    "T": dict(
+        config={
+            "architecture": "Venarax", "vocab": 176, "width": 64, "norm": {"eps": 1e-6},
+            "layers": [
+                {**_attention(4, 2, 32, 16, 0.18, 0.5, 6), "mlp": _mlp(96, 2.0)},
+                {**_latent(3, 16, 16, 24, 48, 0.2, 5000.0, 16, 37), "mlp": _mlp(64, 2.0)},
+                {**_attention(18, 1, 16, 8, 0.25, 0.3, 11), "mlp": _mlp(64, 1.0)},
+            ],
+            "loop": {"start": 1, "stop": 2, "times": 2},
+        },
+        seed=15, page=16,
+    ),
 }
 
 
