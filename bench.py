@@ -547,45 +547,49 @@ def time_venarax_kernels(torch, ops, raw, pk):
         slot = torch.arange(b, dtype=torch.int32, device=dev)
         sk = sinks if vw else None
         seen = min(ctx, window or ctx)
-        t_new = us(lambda: ops.attention_wide(q, kp, vp, o, sk, pos, slot, table, hq, h_kv, dk, dv, window, 0.1))
+        items = b * h_kv * (-(-(hq // h_kv) // 16))
+        splits = max(1, min(6 * 148 // items, -(-seen // 64), 32))  # (the engine's rule: parts/wide_attend.py)
+        scratch = torch.empty(max(1, ops.attention_wide_mma_scratch_words(items, dv, splits)), device=dev)
+        t_new = us(lambda: ops.attention_wide_mma(q, kp, vp, o, sk, pos, slot, table, None, None, b, True, hq, h_kv, dk, dv, window, 0.1,
+                                                  splits, scratch))
+        t_exact = us(lambda: ops.attention_wide(q, kp, vp, o, sk, pos, slot, table, hq, h_kv, dk, dv, window, 0.1), reps=2)
         nbytes = b * seen * h_kv * (dk + (dv if vw else 0)) * 2
-        if vw:  # the dense decoder's exact kernel and its fast decode kernel at the same sizes
+        if vw:  # the dense decoder's decode kernel at the same sizes
             q16, o16 = q.to(bf), torch.empty(b, hq * hd, dtype=bf, device=dev)
-            t_like = us(lambda: ops.attention_generic(q16, kp, vp, o16, pos, slot, table, hq, hkv, hd, None, 0.1))
-            entry(name + "_decode", t_new, t_like, nbytes, like="attention_generic (the exact kernel)")
-            if ops.attention_decode_supports(hd, hq // hkv):
-                t_fast = us(lambda: ops.attention_decode_cluster(q16, kp, vp, o16, pos, slot, table, hq, hkv, hd, None, 0.1, 4,
-                                                                 min(2, ops.attention_decode_cluster_max_stages(hd))))
-                out[name + "_decode"].update(fast_us=round(t_fast, 1), fast_hbm_frac=round(nbytes / t_fast / 1e3 / pk["hbm_gbs"], 3),
-                                             fast="attention_decode_cluster (mma.sync, bfloat16)")
+            t_like = us(lambda: ops.attention_decode_cluster(q16, kp, vp, o16, pos, slot, table, hq, hkv, hd, None, 0.1, 4,
+                                                             min(2, ops.attention_decode_cluster_max_stages(hd))))
+            entry(name + "_decode", t_new, t_like, nbytes, like="attention_decode_cluster (mma.sync, bfloat16)")
         else:
             entry(name + "_decode", t_new, t_new, nbytes, like="(no like kernel: one plane read for keys and values)")
-        # one prompt of 4,096 tokens in one step
+        out[name + "_decode"]["exact_kernel_us"] = round(t_exact, 1)
+        # one prompt of 4,096 tokens in one step, in tiles of 64, 32 or 16 rows
         n = ctx
         posp = torch.arange(n, dtype=torch.int32, device=dev)
         slotp = torch.zeros(n, dtype=torch.int32, device=dev)
         qp, op = rnd(n, hq * dk), torch.empty(n, hq * dv, dtype=bf, device=dev)
-        t_new = us(lambda: ops.attention_wide(qp, kp, vp, op, sk, posp, slotp, table, hq, h_kv, dk, dv, window, 0.1, share_rows=True), reps=2)
+        tile = ops.attention_wide_mma_tile_rows(dv)
+        u0 = torch.arange(0, n, tile, dtype=torch.int32, device=dev)
+        un = torch.full_like(u0, tile)
+        t_new = us(lambda: ops.attention_wide_mma(qp, kp, vp, op, sk, posp, slotp, table, u0, un, u0.numel(), False, hq, h_kv, dk, dv, window, 0.1),
+                   reps=2)
+        t_exact = us(lambda: ops.attention_wide(qp, kp, vp, op, sk, posp, slotp, table, hq, h_kv, dk, dv, window, 0.1, share_rows=True), reps=1)
         pairs = n * (n + 1) // 2 if not window else sum(min(p + 1, window) for p in range(n))
         flops = 2 * pairs * hq * (dk + dv)
-        if vw:
+        if vw and ops.attention_prefill_tc_supports(hd, page):
             qp16, op16 = qp.to(bf), torch.empty(n, hq * hd, dtype=bf, device=dev)
-            t_like = us(lambda: ops.attention_generic(qp16, kp, vp, op16, posp, slotp, table, hq, hkv, hd, None, 0.1, share_rows=True), reps=2)
-            entry(name + "_prefill", t_new, t_like, flops=flops, like="attention_generic (the exact kernel)")
-            if ops.attention_prefill_tc_supports(hd, page):
-                t0 = torch.arange(0, n, 128, dtype=torch.int32, device=dev)
-                tn = torch.full_like(t0, 128)
-                tiles = t0.numel()
-                splits, alone, run_tiles = ops.attention_prefill_tc_plan(tiles, hq, hkv, hd, n, tiles * (tiles + 1) // 2)
-                words = ops.attention_prefill_tc_scratch_words(tiles, hq, hd, splits)
-                scratch = torch.zeros(max(words, 1), dtype=torch.float32, device=dev) if words else None
-                counters = torch.zeros(tiles * hq, dtype=torch.int32, device=dev) if words else None
-                t_fast = us(lambda: ops.attention_prefill_tc(qp16, kp, vp, op16, t0, tn, tiles, posp, slotp, table, hq, hkv, hd, None, 0.1,
-                                                             splits, scratch, counters, alone=alone, run_tiles=run_tiles), reps=2)
-                out[name + "_prefill"].update(fast_us=round(t_fast, 1), fast_tensor_frac=round(flops / t_fast / 1e6 / pk["bf16_tflops"], 4),
-                                              fast="attention_prefill_tc (tcgen05)")
+            t0 = torch.arange(0, n, 128, dtype=torch.int32, device=dev)
+            tn = torch.full_like(t0, 128)
+            tiles = t0.numel()
+            splits_p, alone, run_tiles = ops.attention_prefill_tc_plan(tiles, hq, hkv, hd, n, tiles * (tiles + 1) // 2)
+            words = ops.attention_prefill_tc_scratch_words(tiles, hq, hd, splits_p)
+            scr = torch.zeros(max(words, 1), dtype=torch.float32, device=dev) if words else None
+            counters = torch.zeros(tiles * hq, dtype=torch.int32, device=dev) if words else None
+            t_like = us(lambda: ops.attention_prefill_tc(qp16, kp, vp, op16, t0, tn, tiles, posp, slotp, table, hq, hkv, hd, None, 0.1,
+                                                         splits_p, scr, counters, alone=alone, run_tiles=run_tiles), reps=2)
+            entry(name + "_prefill", t_new, t_like, flops=flops, like="attention_prefill_tc (tcgen05)")
         else:
             entry(name + "_prefill", t_new, t_new, flops=flops, like="(no like kernel)")
+        out[name + "_prefill"]["exact_kernel_us"] = round(t_exact, 1)
         del kp, vp, q, o, qp, op
     # between the input product and the attention: 16,384 rows
     rows = 16384
@@ -614,7 +618,8 @@ def workload_venarax(a, pk):
     from machserve_b200 import ops
 
     out = {}
-    for shape in ("qwen2.5-0.5b", "qwen2.5-1.5b", "qwen2.5-7b"):
+    shapes = sorted(SHAPES) if a.venarax_shapes == "all" else [x.strip() for x in a.venarax_shapes.split(",") if x.strip()]
+    for shape in shapes:
         raw = SHAPES[shape]
         layers = min(raw["num_hidden_layers"], a.layers or 12)  # (layers of equal sizes: twelve tell what all tell)
         res = {"layers": layers}
@@ -630,7 +635,8 @@ def workload_venarax(a, pk):
             b.release_all()
             del b
             free_device_memory()
-        res["kernels"] = time_venarax_kernels(torch, ops, raw, pk)
+        if not a.no_points:
+            res["kernels"] = time_venarax_kernels(torch, ops, raw, pk)
         free_device_memory()
         out[shape] = res
     return {"batch": a.batch, "context": a.context, "prefill_tokens": a.prefill, "dtype": "bf16",
@@ -820,7 +826,8 @@ def main() -> int:
     ap.add_argument("--only", default="headline,fp32,serving_1p5b,mixed_7b",
                     help="which parts to run: headline, fp32, serving_1p5b, mixed_7b (comma separated); venarax, which is not "
                          "among the defaults, times the Venarax design beside the dense decoder at equal layer sizes")
-    ap.add_argument("--no-points", action="store_true", help="skip the further batch sizes and the prefill")
+    ap.add_argument("--no-points", action="store_true", help="skip the further batch sizes and the prefill (venarax: the kernels alone)")
+    ap.add_argument("--venarax-shapes", default="all", help="the shapes of the venarax workload (comma separated), or all")
     ap.add_argument("--profile", default=None, choices=["decode", "prefill", "mixed"],
                     help="which timed region is bracketed by cudaProfilerStart/Stop (for ncu --profile-from-start off)")
     ap.add_argument("--kernel", default=None, choices=["attention_prefill", "gemm"],

@@ -10,7 +10,7 @@
 // temperature.  All arithmetic is float32; the sums of a row happen in an order that depends on the widths alone.
 #include "launch.cuh"
 
-template <typename TC>
+template <typename TC, bool VEC>
 __global__ void __launch_bounds__(256)
 qk_norm_store_kernel(const float* __restrict__ proj, int ld, const float* __restrict__ wq, const float* __restrict__ wk,
                      float eps, float coef, int every, const int* __restrict__ positions, const int* __restrict__ slots,
@@ -26,15 +26,38 @@ qk_norm_store_kernel(const float* __restrict__ proj, int ld, const float* __rest
   const int pos = positions[t];
   const float* row = proj + (size_t)t * ld;
   const int kw = groups * dk, vw = groups * dv;
-  float ss = 0.f;
-  for (int c = threadIdx.x; c < qw; c += blockDim.x) ss += row[c] * row[c];
+  // (four elements at a time where the row, the widths and the weights allow 16-byte accesses; the order of a row's
+  // additions depends on the widths and that alignment alone)
+  const bool vec = VEC && (qw % 4 == 0) && (kw % 4 == 0);
+  float ss = 0.f, sk = 0.f;
+  if (vec) {
+    for (int c = threadIdx.x * 4; c < qw; c += blockDim.x * 4) {
+      const float4 v = *reinterpret_cast<const float4*>(row + c);
+      ss += (v.x * v.x + v.y * v.y) + (v.z * v.z + v.w * v.w);
+    }
+    if (store)
+      for (int c = threadIdx.x * 4; c < kw; c += blockDim.x * 4) {
+        const float4 v = *reinterpret_cast<const float4*>(row + qw + c);
+        sk += (v.x * v.x + v.y * v.y) + (v.z * v.z + v.w * v.w);
+      }
+  } else {
+    for (int c = threadIdx.x; c < qw; c += blockDim.x) ss += row[c] * row[c];
+    if (store)
+      for (int c = threadIdx.x; c < kw; c += blockDim.x) sk += row[qw + c] * row[qw + c];
+  }
   const float q_inv = 1.f / sqrtf(ms_block_sum(ss, scratch) / (float)qw + eps);
   const float temp = coef != 0.f ? 1.f + coef * logf((float)((pos + 1) / every + 1)) : 1.f;
-  for (int c = threadIdx.x; c < qw; c += blockDim.x) q_out[(size_t)t * qw + c] = row[c] * q_inv * wq[c] * temp;
+  if (vec) {
+    for (int c = threadIdx.x * 4; c < qw; c += blockDim.x * 4) {
+      const float4 v = *reinterpret_cast<const float4*>(row + c), w = *reinterpret_cast<const float4*>(wq + c);
+      *reinterpret_cast<float4*>(q_out + (size_t)t * qw + c) =
+          make_float4(v.x * q_inv * w.x * temp, v.y * q_inv * w.y * temp, v.z * q_inv * w.z * temp, v.w * q_inv * w.w * temp);
+    }
+  } else {
+    for (int c = threadIdx.x; c < qw; c += blockDim.x) q_out[(size_t)t * qw + c] = row[c] * q_inv * wq[c] * temp;
+  }
   if (!store) return;
-  ss = 0.f;
-  for (int c = threadIdx.x; c < kw; c += blockDim.x) ss += row[qw + c] * row[qw + c];
-  const float k_inv = 1.f / sqrtf(ms_block_sum(ss, scratch) / (float)kw + eps);
+  const float k_inv = 1.f / sqrtf(ms_block_sum(sk, scratch) / (float)kw + eps);
   const int page = block_table[(size_t)slot * max_pages + pos / page_size];
   if (page < 0 || page >= num_pages) return;
   const size_t at = (size_t)page * groups * page_size + pos % page_size;  // + g * page_size: the row of the (page, head) arrays
@@ -56,16 +79,18 @@ MS_API int ms_qk_norm_store(const float* proj, int ld, const float* wq, const fl
   MS_REQUIRE(tokens > 0 && qw > 0 && groups > 0 && dk > 0 && dv > 0 && every > 0, "qk_norm_store: bad sizes");
   MS_REQUIRE(ld >= qw + (store ? groups * (dk + dv) : 0), "qk_norm_store: rows of %d elements do not hold q, k and v", ld);
   MS_REQUIRE(!store || (max_pages > 0 && num_pages > 0 && page_size > 0 && k_pages && v_pages), "qk_norm_store: no cache to write");
-  if (cache_dtype == MS_F32)
-    MS_LAUNCH_RESULT("qk_norm_store", ms_launch(qk_norm_store_kernel<float>, dim3(tokens), dim3(256), 0, stream, 1, true, proj, ld, wq,
-                                                wk, eps, coef, every, positions, slots, block_table, max_pages, num_pages, page_size,
-                                                q_out, (float*)k_pages, (float*)v_pages, qw, groups, dk, dv, store));
-  else if (cache_dtype == MS_BF16)
-    MS_LAUNCH_RESULT("qk_norm_store", ms_launch(qk_norm_store_kernel<__nv_bfloat16>, dim3(tokens), dim3(256), 0, stream, 1, true, proj,
-                                                ld, wq, wk, eps, coef, every, positions, slots, block_table, max_pages, num_pages,
-                                                page_size, q_out, (__nv_bfloat16*)k_pages, (__nv_bfloat16*)v_pages, qw, groups, dk, dv,
-                                                store));
-  else
+  const bool vec = ld % 4 == 0 && ((uintptr_t)proj | (uintptr_t)wq | (uintptr_t)q_out) % 16 == 0;
+#define MS_QKN(TC, V)                                                                                                      \
+  MS_LAUNCH_RESULT("qk_norm_store", ms_launch(qk_norm_store_kernel<TC, V>, dim3(tokens), dim3(256), 0, stream, 1, true, proj, ld, wq, \
+                                              wk, eps, coef, every, positions, slots, block_table, max_pages, num_pages, page_size,  \
+                                              q_out, (TC*)k_pages, (TC*)v_pages, qw, groups, dk, dv, store))
+  if (cache_dtype == MS_F32) {
+    if (vec) MS_QKN(float, true); else MS_QKN(float, false);
+  } else if (cache_dtype == MS_BF16) {
+    if (vec) MS_QKN(__nv_bfloat16, true); else MS_QKN(__nv_bfloat16, false);
+  } else {
     MS_REQUIRE(false, "qk_norm_store: unknown cache dtype %d", cache_dtype);
+  }
+#undef MS_QKN
   return 0;
 }

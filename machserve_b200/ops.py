@@ -1011,6 +1011,11 @@ def attention_wide_mma_supports(dk: int, dv: int, vw: int, separate_v: bool) -> 
     return bool(lib().ms_attention_wide_mma_supports(int(dk), int(dv), int(vw), int(separate_v)))
 
 
+def attention_wide_mma_tile_rows(dv: int) -> int:
+    """Rows of a portion that one block of the tensor-core form attends (64, 32 or 16, as the value columns leave registers)."""
+    return int(lib().ms_attention_wide_mma_tile_rows(int(dv)))
+
+
 def attention_wide_mma_scratch_words(items: int, dv: int, splits: int) -> int:
     """float32 words of scratch for `items` (decoding rows x key heads x chunks of 16 heads) cut into `splits` runs of keys."""
     fn = lib().ms_attention_wide_mma_scratch_words
@@ -1023,7 +1028,8 @@ def attention_wide_mma(q, k_pages, v_pages, out, sinks, positions, slot_of_token
                        heads: bool, num_heads: int, num_kv_heads: int, dk: int, dv: int, window: Optional[int], scale: float,
                        splits: int = 1, scratch: Optional[torch.Tensor] = None):
     """attention_wide on the tensor cores (mma.sync, bfloat16 cache and output, float32 queries and softmax).
-    heads False: `units` tiles of at most 16 consecutive rows of one sequence, tile u = rows unit_row0[u] .. + unit_rows[u].
+    heads False: `units` tiles of at most attention_wide_mma_tile_rows(dv) consecutive rows of one sequence, tile u = rows
+    unit_row0[u] .. + unit_rows[u].
     heads True: `units` rows that are alone in their sequences (unit_row0[u], or u without a list; -1 for none); the query
     heads that share a key head fill the tensor core's rows, and a row's key tiles are cut into `splits` runs that meet in
     `scratch` (float32, attention_wide_mma_scratch_words).  v_pages may be k_pages itself (a latent cache)."""

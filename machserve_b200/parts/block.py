@@ -77,5 +77,18 @@ class ParallelBlock(Block):
         else:
             self.mixer_norm.forward(residual, as_delta(pending, pairs), xn)
             self.ff_norm.forward(residual, None, xf)
+        # The two halves read different rows and share no scratch memory.  In a captured step they run side by side, as
+        # two branches of the graph: the step's chain of dependent kernels is then the mixer's alone.  (When a step is
+        # launched plainly, the second stream's events would cost the host more than they save.)
+        import torch
+
+        if torch.cuda.is_current_stream_capturing():
+            main, side = torch.cuda.current_stream(), rt.side_stream()
+            side.wait_stream(main)
+            with torch.cuda.stream(side):
+                b = self.feed_forward.forward(ctx, xf)
+            a = self.mixer.forward(ctx, xn, cache, owns_cache)
+            main.wait_stream(side)
+            return DeltaPair(a, b)
         a = self.mixer.forward(ctx, xn, cache, owns_cache)
         return DeltaPair(a, self.feed_forward.forward(ctx, xf))

@@ -7,19 +7,21 @@ import torch
 from .. import ops
 from .base import WorkPlan
 
-PLAN = "row_tiles16"  # the key of the work lists: every such mixer of a model shares them
-TILE = 16             # rows of a portion that one block of the tensor-core kernel attends
+PLAN = "row_tiles"    # the key of the work lists: every such mixer of a model shares them
+TILES = (64, 32, 16)  # rows of a portion that one block of the tensor-core kernel attends: by the width of the values
 CONTEXT_BUCKET = 512  # a decoding row's run of keys is chosen from the longest context rounded up to this
+BLOCKS_PER_SM = 6     # decoding rows are cut into runs of keys until the launch has about this many blocks per SM
 
 
 def plan_words(max_rows: int, max_seqs: int) -> int:
-    return 4 * max_seqs + 16 + 2 * (max_rows // TILE + max_seqs + 8)
+    return 4 * max_seqs + 16 + sum(2 * (max_rows // t + max_seqs + 8) for t in TILES)
 
 
 def plan(step) -> WorkPlan:
     """Rows that are alone in their sequence (decoding) go to the form whose 16 rows are the query heads of a token;
-    portions of prompts are cut into tiles of up to 16 consecutive rows."""
-    single, t0, tn = [], [], []
+    portions of prompts are cut into tiles of up to 64, 32 and 16 consecutive rows (a list for each size)."""
+    single = []
+    t0, tn = {t: [] for t in TILES}, {t: [] for t in TILES}
     longest = 0
     for row, n, start in zip(step.row0, step.count, step.start):
         if n == 0:
@@ -28,21 +30,26 @@ def plan(step) -> WorkPlan:
             single.append(row)
             longest = max(longest, start + 1)
         else:
-            for a in range(0, n, TILE):
-                t0.append(row + a)
-                tn.append(min(TILE, n - a))
+            for t in TILES:
+                for a in range(0, n, t):
+                    t0[t].append(row + a)
+                    tn[t].append(min(t, n - a))
     cls = -(-longest // CONTEXT_BUCKET)
     if step.bucketed:  # lists of a few lengths (an entry of no rows does nothing), the context class a power of two
-        pad = -len(t0) % 8
-        t0 += [0] * pad
-        tn += [0] * pad
+        for t in TILES:
+            pad = -len(t0[t]) % (512 // t)
+            t0[t] += [0] * pad
+            tn[t] += [0] * pad
         if single:
             want = 16
             while want < len(single):
                 want *= 4
             single += [-1] * (want - len(single))
         cls = 1 << (cls - 1).bit_length() if cls > 0 else 0
-    return WorkPlan({"single_rows": single, "tile_row0": t0, "tile_rows": tn}, (cls,))
+    lists = {"single_rows": single}
+    for t in TILES:
+        lists[f"tile{t}_row0"], lists[f"tile{t}_rows"] = t0[t], tn[t]
+    return WorkPlan(lists, (cls,))
 
 
 def supports(rt, dk: int, dv: int, vw: int, separate_v: bool) -> bool:
@@ -51,18 +58,19 @@ def supports(rt, dk: int, dv: int, vw: int, separate_v: bool) -> bool:
 
 def attend(ctx, rt, fast: bool, table, q, k_pages, v_pages, out, sinks, hq: int, hkv: int, dk: int, dv: int, window, scale: float):
     """Every row of q over its sequence's pages: on the tensor cores when the widths allow it in bfloat16 (decoding rows
-    with their key tiles cut into as many runs as fill the GPU, portions in tiles of 16 rows), else the exact kernel."""
+    with their key tiles cut into as many runs as fill the GPU, portions in tiles of 64, 32 or 16 rows), else the exact kernel."""
     if not fast:
         return ops.attention_wide(q, k_pages, v_pages, out, sinks, ctx.positions, ctx.slot_of_token, table, hq, hkv,
                                   dk, dv, window, scale, share_rows=ctx.max_query_len > 1)
     work = ctx.work[PLAN]
-    singles, tiles = work.sizes["single_rows"], work.sizes["tile_row0"]
+    tile = ops.attention_wide_mma_tile_rows(dv)
+    singles, tiles = work.sizes["single_rows"], work.sizes[f"tile{tile}_row0"]
     if singles:
         items = singles * hkv * (-(-(hq // hkv) // 16))
         keys = work.shape[0] * CONTEXT_BUCKET
         if window:
             keys = min(keys, window + 63)
-        splits = max(1, min(2 * rt.sm_count // items, -(-keys // 64), 32))
+        splits = max(1, min(BLOCKS_PER_SM * rt.sm_count // items, -(-keys // 64), 32))
         scratch = None
         if splits > 1:
             scratch = rt.workspace.get("wide_attend.splits", (ops.attention_wide_mma_scratch_words(items, dv, splits),), torch.float32)
@@ -70,8 +78,8 @@ def attend(ctx, rt, fast: bool, table, q, k_pages, v_pages, out, sinks, hq: int,
         ops.attention_wide_mma(q, k_pages, v_pages, out, sinks, ctx.positions, ctx.slot_of_token, table, rows, None, singles, True,
                                hq, hkv, dk, dv, window, scale, splits, scratch)
     if tiles:
-        ops.attention_wide_mma(q, k_pages, v_pages, out, sinks, ctx.positions, ctx.slot_of_token, table, work.lists["tile_row0"],
-                               work.lists["tile_rows"], tiles, False, hq, hkv, dk, dv, window, scale)
+        ops.attention_wide_mma(q, k_pages, v_pages, out, sinks, ctx.positions, ctx.slot_of_token, table, work.lists[f"tile{tile}_row0"],
+                               work.lists[f"tile{tile}_rows"], tiles, False, hq, hkv, dk, dv, window, scale)
     return out
 
 

@@ -193,7 +193,7 @@ def test_tensor_core_attention_with_sink_and_unequal_widths(dk, dv, hq, hkv, win
     assert ops.attention_wide_mma_supports(dk, dv, vd.shape[3], not latent)
     sinks = rng.normal(size=hq).astype(np.float32) * 2 if sink else None
     scale = 0.5 / np.sqrt(dk)
-    # rows 0..36: positions 100..136 of sequence 0 (tiles of 16, 16 and 5 rows); row 37: the last position of sequence 0,
+    # rows 0..36: positions 100..136 of sequence 0 (in tiles of as many rows as a block takes); row 37: the last position of sequence 0,
     # decoded; rows 38..40: the first three positions of sequence 1; row 41: position 40 of sequence 1, decoded
     rows = [(0, p) for p in range(100, 137)] + [(0, 149)] + [(1, p) for p in range(3)] + [(1, 40)]
     q = rng.normal(size=(len(rows), hq, dk)).astype(np.float32)
@@ -206,10 +206,14 @@ def test_tensor_core_attention_with_sink_and_unequal_widths(dk, dv, hq, hkv, win
         idx = [i for i, (ss, _) in enumerate(rows) if ss == s]
         want[idx] = _plain_attend(q_held[idx], ks[s], vs[s], [rows[i][1] for i in idx], window, scale, sinks, hq // hkv)
     sk = None if sinks is None else _dev(sinks)
+    tile = ops.attention_wide_mma_tile_rows(dv)
+    assert tile == (64 if dv <= 128 else 32 if dv <= 256 else 16)
+    t0 = list(range(0, 37, tile)) + [38, 0]
+    tn = [min(tile, 37 - a) for a in range(0, 37, tile)] + [3, 0]
     for splits in (1, 3):
         out = torch.full((len(rows), hq * dv), 7.0, dtype=bf, device="cuda")
-        ops.attention_wide_mma(_dev(q).view(len(rows), hq * dk), kd, vd, out, sk, pos, slot, _dev(table), ints([0, 16, 32, 38, 0]),
-                               ints([16, 16, 5, 3, 0]), 5, False, hq, hkv, dk, dv, window, scale)
+        ops.attention_wide_mma(_dev(q).view(len(rows), hq * dk), kd, vd, out, sk, pos, slot, _dev(table), ints(t0), ints(tn), len(t0), False,
+                               hq, hkv, dk, dv, window, scale)
         items = 3 * hkv * (-(-(hq // hkv) // 16))
         scratch = torch.empty(max(1, ops.attention_wide_mma_scratch_words(items, dv, splits)), device="cuda")
         ops.attention_wide_mma(_dev(q).view(len(rows), hq * dk), kd, vd, out, sk, pos, slot, _dev(table), ints([37, -1, 41]), None, 3, True,
