@@ -208,11 +208,18 @@ __device__ __forceinline__ void atc_row_probs(unsigned (&r)[ATC_KEYS], int rlo, 
 // split order (so the result does not depend on who came last), writes the output and clears the counter.
 // No block waits for another.
 template <int HD>
-__device__ __forceinline__ void atc_finish(unsigned tmem_o_lane, bool have_o, float m, float l, int row, int nrows,
+__device__ __forceinline__ void atc_finish(unsigned tmem_o_lane, bool have_o, float m, float l, float sink2, int row, int nrows,
                                            __nv_bfloat16* dst, int nsplit, int split, float* item_scratch, int* counter,
                                            int bar_id, volatile int* last_flag) {
+  // sink2: a sink's exponent (sink * log2 e) that joins the softmax's denominator without a value, or -inf for none
   if (nsplit <= 1) {
-    const float inv = l > 0.f ? 1.f / l : 0.f;
+    float sum = l, f = 1.f;
+    if (sink2 > -INFINITY) {  // against the reference m, or as the reference if it is larger
+      const float top = fmaxf(m, sink2);
+      f = atc_exp2(m - top);
+      sum = l * f + atc_exp2(sink2 - top);
+    }
+    const float inv = sum > 0.f ? f / sum : 0.f;
 #pragma unroll
     for (int c = 0; c < HD; c += 32) {
       unsigned v[32];
@@ -266,7 +273,8 @@ __device__ __forceinline__ void atc_finish(unsigned tmem_o_lane, bool have_o, fl
     ms[s] = s < nsplit ? __ldcg(item_scratch + (size_t)s * ATC_SPLIT_WORDS(HD) + (size_t)HD * ATC_ROWS + row) : -INFINITY;
     top = fmaxf(top, ms[s]);
   }
-  float sum = 0.f;
+  top = fmaxf(top, sink2);
+  float sum = sink2 > -INFINITY ? atc_exp2(sink2 - top) : 0.f;
 #pragma unroll
   for (int s = 0; s < ATC_MAX_SPLITS; ++s) {
     const float ls = s < nsplit ? __ldcg(item_scratch + (size_t)s * ATC_SPLIT_WORDS(HD) + (size_t)(HD + 1) * ATC_ROWS + row) : 0.f;
@@ -322,7 +330,7 @@ attention_prefill_tc_single_kernel(const __grid_constant__ CUtensorMap map_q, co
                             const int* __restrict__ positions, const int* __restrict__ slot_of_token,
                             const int* __restrict__ block_table, int max_pages, int num_pages, int hq, int hkv,
                             int page_size, int window, float scale_log2, int num_runs, int run_tiles, float* __restrict__ scratch,
-                            int* __restrict__ counters) {
+                            int* __restrict__ counters, const float* __restrict__ sinks) {
   constexpr int PANELS = HD / 64;          // 64-column panels of Q, K and V
   constexpr int PANEL_BYTES = 128 * 128;   // 128 rows of 128 bytes
   constexpr int KV_BYTES = PANELS * PANEL_BYTES;
@@ -567,7 +575,8 @@ attention_prefill_tc_single_kernel(const __grid_constant__ CUtensorMap map_q, co
     asm volatile("bar.sync 1, 128;\n" ::: "memory");
     if (!sh->group_bad && active) {
       const size_t item = (size_t)tile_id * hq + h;
-      atc_finish<HD>(tmem_o + lane_addr, ntiles > 0, m, l, row, nrows, out + ((size_t)(row0 + row) * hq + h) * HD, nsplit, split,
+      atc_finish<HD>(tmem_o + lane_addr, ntiles > 0, m, l, sinks ? sinks[h] * ATC_LOG2E : -INFINITY, row, nrows,
+                     out + ((size_t)(row0 + row) * hq + h) * HD, nsplit, split,
                      scratch + item * nruns * ATC_SPLIT_WORDS(HD), counters + item, 1, &sh->last_flag);
       atc_fence_before();
     }
@@ -603,7 +612,7 @@ attention_prefill_tc_pair_kernel(const __grid_constant__ CUtensorMap map_q, cons
                             const int* __restrict__ positions, const int* __restrict__ slot_of_token,
                             const int* __restrict__ block_table, int max_pages, int num_pages, int hq, int hkv,
                             int page_size, int window, float scale_log2, int num_runs, int run_tiles, int alone, float* __restrict__ scratch,
-                            int* __restrict__ counters) {
+                            int* __restrict__ counters, const float* __restrict__ sinks) {
   constexpr int PANELS = HD / 64;          // 64-column panels of Q, K and V
   constexpr int PANEL_BYTES = 128 * 128;   // 128 rows of 128 bytes
   constexpr int KV_BYTES = PANELS * PANEL_BYTES;
@@ -871,7 +880,8 @@ attention_prefill_tc_pair_kernel(const __grid_constant__ CUtensorMap map_q, cons
     asm volatile("bar.sync %0, 128;\n" ::"r"(1 + x) : "memory");
     if (!sh->group_bad[x] && (x == 0 || has_b) && active) {
       const size_t item = (size_t)tile_id * hq + head_a + x;
-      atc_finish<HD>(tmem_o + lane_addr, steps > 0, m, l, row, nrows, out + ((size_t)(row0 + row) * hq + head_a + x) * HD, nsplit,
+      atc_finish<HD>(tmem_o + lane_addr, steps > 0, m, l, sinks ? sinks[head_a + x] * ATC_LOG2E : -INFINITY, row, nrows,
+                     out + ((size_t)(row0 + row) * hq + head_a + x) * HD, nsplit,
                      split, scratch + item * nruns * ATC_SPLIT_WORDS(HD), counters + item, 1 + x, &sh->last_flag[x]);
       atc_fence_before();
     }
@@ -914,7 +924,7 @@ static int atc_make_map(CUtensorMap* map, const void* base, long long rows, int 
 static int atc_launch_single(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, void* out, const int* tile_row0,
                              const int* tile_rows, int num_tiles, const int* positions, const int* slot_of_token,
                              const int* block_table, int max_pages, int num_pages, int hq, int hkv, int page_size, int window,
-                             float scale, int splits, int run_tiles, float* scratch, int* counters, cudaStream_t stream) {
+                             float scale, int splits, int run_tiles, float* scratch, int* counters, const float* sinks, cudaStream_t stream) {
   const size_t smem = 1024 + 1024 + (size_t)16384 * 4;
   auto kern = attention_prefill_tc_single_kernel<64>;
   static bool configured = false;
@@ -927,7 +937,7 @@ static int atc_launch_single(const CUtensorMap& mq, const CUtensorMap& mk, const
   dim3 grid(hq, num_tiles * splits);
   kern<<<grid, ATC_THREADS, smem, stream>>>(mq, mk, mv, (__nv_bfloat16*)out, tile_row0, tile_rows, positions, slot_of_token,
                                             block_table, max_pages, num_pages, hq, hkv, page_size, window, scale * ATC_LOG2E,
-                                            splits, run_tiles, scratch, counters);
+                                            splits, run_tiles, scratch, counters, sinks);
   MS_LAUNCH_CHECK("attention_prefill_tc");
   return 0;
 }
@@ -936,7 +946,7 @@ template <int HD>
 static int atc_launch_pair(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, void* out, const int* tile_row0,
                            const int* tile_rows, int num_tiles, const int* positions, const int* slot_of_token,
                            const int* block_table, int max_pages, int num_pages, int hq, int hkv, int page_size, int window,
-                           float scale, int splits, int run_tiles, int alone, float* scratch, int* counters, cudaStream_t stream) {
+                           float scale, int splits, int run_tiles, int alone, float* scratch, int* counters, const float* sinks, cudaStream_t stream) {
   // two heads' Q, two stages of K and of V (194 KB at head size 128); never less than half an SM's shared memory, so
   // that a block has the SM and all of its tensor memory to itself
   size_t smem = 1024 + 1024 + (size_t)(HD / 64) * 16384 * 6;
@@ -954,7 +964,7 @@ static int atc_launch_pair(const CUtensorMap& mq, const CUtensorMap& mk, const C
   dim3 grid(hkv * (alone ? groups : (groups + 1) / 2), num_tiles * splits);
   kern<<<grid, ATC_PAIR_THREADS, smem, stream>>>(mq, mk, mv, (__nv_bfloat16*)out, tile_row0, tile_rows, positions, slot_of_token,
                                                  block_table, max_pages, num_pages, hq, hkv, page_size, window, scale * ATC_LOG2E,
-                                                 splits, run_tiles, alone, scratch, counters);
+                                                 splits, run_tiles, alone, scratch, counters, sinks);
   MS_LAUNCH_CHECK("attention_prefill_tc");
   return 0;
 }
@@ -1060,12 +1070,13 @@ MS_API void ms_attention_prefill_tc_plan(int num_tiles, int hq, int hkv, int hd,
 // key tiles of every item go to that many blocks, which meet in `scratch` (ms_attention_prefill_tc_scratch_words) and
 // count themselves in `counters` (num_tiles * hq of them, all zero).  `alone` (head size 128): a block takes one head, not two.
 // `run_tiles` > 0: an item is cut only into as many runs as keep a run at that many key tiles at most (0: always `splits`).
-MS_API int ms_attention_prefill_tc(const void* q, const void* k_pages, const void* v_pages, void* out, int total_rows,
-                                   const int* tile_row0, const int* tile_rows, int num_tiles, const int* positions,
-                                   const int* slot_of_token, const int* block_table, int max_pages, int num_pages, int hq,
-                                   int hkv, int hd, int page_size, int window, float scale, int splits, int alone,
-                                   int run_tiles, float* scratch, long long scratch_words, int* counters,
-                                   long long num_counters, cudaStream_t stream) {
+// sinks: float32 [hq], one number per head whose exponential joins the softmax's denominator without a value; or null.
+MS_API int ms_attention_prefill_tc_sinks(const void* q, const void* k_pages, const void* v_pages, void* out, int total_rows,
+                                         const int* tile_row0, const int* tile_rows, int num_tiles, const int* positions,
+                                         const int* slot_of_token, const int* block_table, int max_pages, int num_pages, int hq,
+                                         int hkv, int hd, int page_size, int window, float scale, int splits, int alone,
+                                         int run_tiles, float* scratch, long long scratch_words, int* counters,
+                                         long long num_counters, const float* sinks, cudaStream_t stream) {
   if (num_tiles == 0) return 0;
   MS_REQUIRE(num_tiles > 0 && total_rows > 0 && hq > 0 && hkv > 0 && hq % hkv == 0, "attention_prefill_tc: bad sizes");
   MS_REQUIRE(ms_attention_prefill_tc_supports(hd, page_size),
@@ -1085,7 +1096,18 @@ MS_API int ms_attention_prefill_tc(const void* q, const void* k_pages, const voi
   if (int rc = atc_make_map(&mv, v_pages, cache_rows, hd, hd, box)) return rc;
   if (hd == 64)
     return atc_launch_single(mq, mk, mv, out, tile_row0, tile_rows, num_tiles, positions, slot_of_token, block_table, max_pages,
-                             num_pages, hq, hkv, page_size, window, scale, splits, run_tiles, scratch, counters, stream);
+                             num_pages, hq, hkv, page_size, window, scale, splits, run_tiles, scratch, counters, sinks, stream);
   return atc_launch_pair<128>(mq, mk, mv, out, tile_row0, tile_rows, num_tiles, positions, slot_of_token, block_table, max_pages,
-                              num_pages, hq, hkv, page_size, window, scale, splits, run_tiles, alone ? 1 : 0, scratch, counters, stream);
+                              num_pages, hq, hkv, page_size, window, scale, splits, run_tiles, alone ? 1 : 0, scratch, counters, sinks, stream);
+}
+
+MS_API int ms_attention_prefill_tc(const void* q, const void* k_pages, const void* v_pages, void* out, int total_rows,
+                                   const int* tile_row0, const int* tile_rows, int num_tiles, const int* positions,
+                                   const int* slot_of_token, const int* block_table, int max_pages, int num_pages, int hq,
+                                   int hkv, int hd, int page_size, int window, float scale, int splits, int alone,
+                                   int run_tiles, float* scratch, long long scratch_words, int* counters,
+                                   long long num_counters, cudaStream_t stream) {
+  return ms_attention_prefill_tc_sinks(q, k_pages, v_pages, out, total_rows, tile_row0, tile_rows, num_tiles, positions, slot_of_token,
+                                       block_table, max_pages, num_pages, hq, hkv, hd, page_size, window, scale, splits, alone,
+                                       run_tiles, scratch, scratch_words, counters, num_counters, nullptr, stream);
 }

@@ -73,7 +73,7 @@ class _Signatures:
     ms_concat_streams = [P, P, I, P, I, P, P, I, I, I, P]
     ms_glu_clamped = [P, P, I, I, I, F, F, F, P]
     ms_sigmoid_gate_mul = [P, I, P, I, P, I, I, I, P]
-    ms_qk_norm_store = [P, I, P, P, F, F, I, P, P, P, I, I, I, P, P, P, I, I, I, I, I, I, I, P]
+    ms_qk_norm_store = [P, I, P, P, F, F, I, P, P, P, I, I, I, P, P, P, P, I, I, I, I, I, I, I, P]
     ms_latent_encode = [P, I, I, P, F, P, I, I, P, P, P, I, I, I, P, P, I, P, I, I, I, I, I, I, I, P]
     ms_attention_wide = [P, P, P, P, I, P, P, P, P, I, I, I, I, I, I, I, I, I, I, F, I, P]
     ms_attention_wide_mma = [P, P, P, P, P, P, P, P, I, I, P, P, I, I, I, I, I, I, I, I, I, F, I, P, P]
@@ -86,6 +86,7 @@ class _Signatures:
     ms_attention_decode_cluster_rope = [P, I, P, P, I, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, I, I, I, I, I, P, LL, P, I, P]
     ms_attention_prefill_tc = [P, P, P, P, I, P, P, I, P, P, P, I, I, I, I, I, I, I, F, I, I, I, P, LL, P, LL, P]
     ms_attention_prefill_tc_plan = [I, I, I, I, I, I, I, P]
+    ms_attention_prefill_tc_sinks = [P, P, P, P, I, P, P, I, P, P, P, I, I, I, I, I, I, I, F, I, I, I, P, LL, P, LL, P, P]
     ms_attention_prefill = [P, P, P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, P]
     ms_gemm_small_m = [P, I, P, P, I, I, I, I, I, I, P]
     ms_gemm_small_m_silu_mul = [P, I, P, P, P, I, I, I, I, I, P]
@@ -813,16 +814,18 @@ def attention_prefill_tc_scratch_words(num_tiles: int, num_heads: int, head_dim:
 
 def attention_prefill_tc(q, k_pages, v_pages, out, tile_row0, tile_rows, num_tiles, positions, slot_of_token, block_table,
                          num_heads, num_kv_heads, head_dim, window, scale, splits=1, scratch=None, counters=None, alone=False,
-                         run_tiles=0):
+                         run_tiles=0, sinks=None):
     """Paged causal attention for tiles of up to 128 consecutive rows of one sequence on tcgen05 tensor cores
     (TMA-fed, scores in tensor memory and taken into registers a row per thread, probabilities back into tensor
     memory, outputs accumulated there over all key tiles).  Head sizes 64 (one head per block) and 128 (two heads of a
     group per block, which share the keys and values), page sizes 8, 16, 32, ...  With `splits` > 1 the key tiles of
     every (tile, head) go to that many blocks, which meet in `scratch` (float32) and count themselves in `counters`
     (int32, num_tiles * num_heads of them, all zero before and after).  `alone` (head size 128): one head per block.
-    `run_tiles` > 0: only items with more key tiles are cut, into runs of at most that many."""
+    `run_tiles` > 0: only items with more key tiles are cut, into runs of at most that many.  `sinks` (float32, one per
+    head): exp(sink) joins every row's softmax denominator and has no value."""
     _need(q.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and k_pages.dtype == torch.bfloat16,
           "attention_prefill_tc: bfloat16 only")
+    _need(sinks is None or (sinks.dtype == torch.float32 and sinks.numel() == num_heads), "attention_prefill_tc: bad sinks")
     _need(q.is_contiguous() and out.is_contiguous() and k_pages.is_contiguous() and v_pages.is_contiguous(),
           "attention_prefill_tc: bad layout")
     _need(tuple(k_pages.shape[1:]) == (num_kv_heads, k_pages.shape[2], head_dim), "attention_prefill_tc: bad page shape")
@@ -832,12 +835,12 @@ def attention_prefill_tc(q, k_pages, v_pages, out, tile_row0, tile_rows, num_til
     _need(scratch is None or (scratch.dtype == torch.float32 and scratch.is_contiguous()), "attention_prefill_tc: scratch must be float32")
     _need(counters is None or (counters.dtype == torch.int32 and counters.is_contiguous()), "attention_prefill_tc: counters must be int32")
     _check(
-        lib().ms_attention_prefill_tc(
+        lib().ms_attention_prefill_tc_sinks(
             _ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(out), q.shape[0], _ptr(tile_row0), _ptr(tile_rows), int(num_tiles),
             _ptr(positions), _ptr(slot_of_token), _ptr(block_table), block_table.shape[1], k_pages.shape[0], num_heads,
             num_kv_heads, head_dim, k_pages.shape[2], int(window or 0), float(scale), int(splits), 1 if alone else 0, int(run_tiles), _ptr(scratch),
             scratch.numel() if scratch is not None else 0, _ptr(counters), counters.numel() if counters is not None else 0,
-            _stream(),
+            _ptr(sinks), _stream(),
         ),
         "attention_prefill_tc",
     )
@@ -932,13 +935,16 @@ def sigmoid_gate_mul(x, gate, out):
 
 
 def qk_norm_store(proj, wq, wk, eps, coef, every, positions, slot_of_token, block_table, q_out, k_pages, v_pages,
-                  groups: int, dk: int, dv: int, store: bool = True):
+                  groups: int, dk: int, dv: int, store: bool = True, q_half=None):
     """Unit-rms norm of the whole q and of the whole k projection with weights, query temperature
     1 + coef * ln(floor((p + 1) / every) + 1), q to q_out (float32), k and v into their pages.
 
     proj float32 [T, >= qw + groups*(dk + dv)] = [q | k | v]; wq [qw], wk [groups*dk] float32; q_out float32 [T, qw];
-    k pages [pages, groups, page, dk], v pages [pages, groups, page, dv]."""
+    k pages [pages, groups, page, dk], v pages [pages, groups, page, dv].  `q_half`: bfloat16 [T, qw], a rounded copy
+    of the queries for a kernel that reads them so."""
     t, qw = q_out.shape
+    _need(q_half is None or (q_half.dtype == torch.bfloat16 and q_half.is_contiguous() and tuple(q_half.shape) == (t, qw)),
+          "qk_norm_store: bad bfloat16 copy of the queries")
     _need(proj.dtype == torch.float32 and proj.stride(1) == 1 and q_out.dtype == torch.float32 and q_out.is_contiguous(),
           "qk_norm_store: bad layout")
     _need(wq.dtype == torch.float32 and wq.numel() == qw and wk.dtype == torch.float32 and wk.numel() == groups * dk,
@@ -951,7 +957,7 @@ def qk_norm_store(proj, wq, wk, eps, coef, every, positions, slot_of_token, bloc
     _check(lib().ms_qk_norm_store(
         _ptr(proj), proj.stride(0), _ptr(wq), _ptr(wk), float(eps), float(coef), int(every), _ptr(positions), _ptr(slot_of_token),
         _ptr(block_table), block_table.shape[1] if store else 0, k_pages.shape[0] if store else 0, k_pages.shape[2] if store else 0,
-        _ptr(q_out), _ptr(k_pages if store else None), _ptr(v_pages if store else None), _code(k_pages) if store else F32,
+        _ptr(q_out), _ptr(q_half), _ptr(k_pages if store else None), _ptr(v_pages if store else None), _code(k_pages) if store else F32,
         t, qw, groups, dk, dv, int(store), _stream()), "qk_norm_store")
     return q_out
 

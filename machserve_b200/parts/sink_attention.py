@@ -77,10 +77,14 @@ class SinkAttention(wide_attend.WideAttendPlan, Mixer):
         q = ws.get("sink_attn.q", (t, self.qw), torch.float32)
         k_pages, v_pages = cache.planes["k"], cache.planes["v"]
         table = cache.block_table(ctx)
+        # a step with portions of prompts: their rows go to the tcgen05 kernel where it covers the sizes; it reads bfloat16 queries
+        q_half = None
+        if self.fast and ctx.max_query_len > 1 and wide_attend.tcgen05_covers(rt, self.dk, self.dv, k_pages.shape[2]):
+            q_half = ws.get("sink_attn.q_half", (t, self.qw), rt.dtype)
         ops.qk_norm_store(proj, self.q_norm, self.k_norm, self.eps, self.coef, self.every, ctx.positions, ctx.slot_of_token, table,
-                          q, k_pages, v_pages, self.hkv, self.dk, self.dv, store=owns_cache)
+                          q, k_pages, v_pages, self.hkv, self.dk, self.dv, store=owns_cache, q_half=q_half)
         out = ws.get("sink_attn.out", (t, self.hq * self.dv), rt.dtype)
         wide_attend.attend(ctx, rt, self.fast, table, q, k_pages, v_pages, out, self.sinks, self.hq, self.hkv, self.dk, self.dv,
-                           self.window, self.scale)
+                           self.window, self.scale, q_half=q_half)
         delta = ws.get("mixer.delta_f32", (t, self.hidden), torch.float32)
         return ops.linear(out, self.w_o, None, delta)

@@ -8,7 +8,7 @@ from .. import ops
 from .base import WorkPlan
 
 PLAN = "row_tiles"    # the key of the work lists: every such mixer of a model shares them
-TILES = (64, 32, 16)  # rows of a portion that one block of the tensor-core kernel attends: by the width of the values
+TILES = (128, 64, 32, 16)  # rows of a portion that one block attends: 128 in the tcgen05 kernel, else by the width of the values
 CONTEXT_BUCKET = 512  # a decoding row's run of keys is chosen from the longest context rounded up to this
 BLOCKS_PER_SM = 6     # decoding rows are cut into runs of keys until the launch has about this many blocks per SM
 
@@ -22,7 +22,7 @@ def plan(step) -> WorkPlan:
     portions of prompts are cut into tiles of up to 64, 32 and 16 consecutive rows (a list for each size)."""
     single = []
     t0, tn = {t: [] for t in TILES}, {t: [] for t in TILES}
-    longest = 0
+    longest = longest_portion = key_tiles = 0
     for row, n, start in zip(step.row0, step.count, step.start):
         if n == 0:
             continue
@@ -30,11 +30,16 @@ def plan(step) -> WorkPlan:
             single.append(row)
             longest = max(longest, start + 1)
         else:
+            longest_portion = max(longest_portion, start + n)
+            for a in range(0, n, 128):  # tiles of 128 keys that the tiles of 128 rows see, in all
+                key_tiles += (start + a + min(128, n - a) - 1) // 128 + 1
             for t in TILES:
                 for a in range(0, n, t):
                     t0[t].append(row + a)
                     tn[t].append(min(t, n - a))
     cls = -(-longest // CONTEXT_BUCKET)
+    cls_portion = -(-longest_portion // CONTEXT_BUCKET)
+    mean_tiles = -(-key_tiles // (2 * len(t0[128]))) * 2 if t0[128] else 0
     if step.bucketed:  # lists of a few lengths (an entry of no rows does nothing), the context class a power of two
         for t in TILES:
             pad = -len(t0[t]) % (512 // t)
@@ -46,17 +51,46 @@ def plan(step) -> WorkPlan:
                 want *= 4
             single += [-1] * (want - len(single))
         cls = 1 << (cls - 1).bit_length() if cls > 0 else 0
+        cls_portion = 1 << (cls_portion - 1).bit_length() if cls_portion > 0 else 0
+        mean_tiles = 4 * cls_portion  # (the bound that the portions' class gives: 512 keys are 4 tiles)
     lists = {"single_rows": single}
     for t in TILES:
         lists[f"tile{t}_row0"], lists[f"tile{t}_rows"] = t0[t], tn[t]
-    return WorkPlan(lists, (cls,))
+    return WorkPlan(lists, (cls, cls_portion, mean_tiles))
 
 
 def supports(rt, dk: int, dv: int, vw: int, separate_v: bool) -> bool:
     return rt.dtype == torch.bfloat16 and ops.attention_wide_mma_supports(dk, dv, vw, separate_v)
 
 
-def attend(ctx, rt, fast: bool, table, q, k_pages, v_pages, out, sinks, hq: int, hkv: int, dk: int, dv: int, window, scale: float):
+def tcgen05_covers(rt, dk: int, dv: int, page_size: int) -> bool:
+    """Whether portions of prompts can go to the framework's tcgen05 attention: keys and values of one width, 64 or 128."""
+    return rt.dtype == torch.bfloat16 and dk == dv and dk in (64, 128) and ops.attention_prefill_tc_supports(dk, page_size)
+
+
+def attend_portions_tcgen05(ctx, rt, table, q_half, k_pages, v_pages, out, sinks, hq: int, hkv: int, hd: int, window, scale: float):
+    """The rows of prompt portions on the tcgen05 kernel, in tiles of 128 rows; the kernel's own plan says into how many
+    runs the key tiles of a tile of rows are cut so that the launch fills the GPU."""
+    work = ctx.work[PLAN]
+    n_tiles = work.sizes["tile128_row0"]
+    if not n_tiles:
+        return out
+    max_keys = work.shape[1] * CONTEXT_BUCKET
+    if window:
+        max_keys = min(max_keys, window + 128)
+    splits, alone, run_tiles = ops.attention_prefill_tc_plan(n_tiles, hq, hkv, hd, max_keys, work.shape[2] * n_tiles)
+    scratch = counters = None
+    if splits > 1:
+        words = ops.attention_prefill_tc_scratch_words(n_tiles, hq, hd, splits)
+        scratch = rt.workspace.get("wide_attend.tc_splits", (words,), torch.float32)
+        counters = rt.workspace.get("wide_attend.tc_counters", (n_tiles * hq,), torch.int32, zero=True)
+    return ops.attention_prefill_tc(q_half, k_pages, v_pages, out, work.lists["tile128_row0"], work.lists["tile128_rows"], n_tiles,
+                                    ctx.positions, ctx.slot_of_token, table, hq, hkv, hd, window, scale, splits, scratch, counters,
+                                    alone=alone, run_tiles=run_tiles, sinks=sinks)
+
+
+def attend(ctx, rt, fast: bool, table, q, k_pages, v_pages, out, sinks, hq: int, hkv: int, dk: int, dv: int, window, scale: float,
+           q_half=None):
     """Every row of q over its sequence's pages: on the tensor cores when the widths allow it in bfloat16 (decoding rows
     with their key tiles cut into as many runs as fill the GPU, portions in tiles of 64, 32 or 16 rows), else the exact kernel."""
     if not fast:
@@ -77,7 +111,9 @@ def attend(ctx, rt, fast: bool, table, q, k_pages, v_pages, out, sinks, hq: int,
         rows = None if tiles == 0 and singles == q.shape[0] else work.lists["single_rows"]
         ops.attention_wide_mma(q, k_pages, v_pages, out, sinks, ctx.positions, ctx.slot_of_token, table, rows, None, singles, True,
                                hq, hkv, dk, dv, window, scale, splits, scratch)
-    if tiles:
+    if q_half is not None:  # portions on the tcgen05 kernel (the part has made sure that it covers the sizes)
+        attend_portions_tcgen05(ctx, rt, table, q_half, k_pages, v_pages, out, sinks, hq, hkv, dk, window, scale)
+    elif tiles:
         ops.attention_wide_mma(q, k_pages, v_pages, out, sinks, ctx.positions, ctx.slot_of_token, table, work.lists[f"tile{tile}_row0"],
                                work.lists[f"tile{tile}_rows"], tiles, False, hq, hkv, dk, dv, window, scale)
     return out

@@ -438,19 +438,21 @@ def test_long_decoding(model_root, name):
         assert_close(got["a"], _want(d, dtype, toks), _tol(dtype), f"{name} {dtype} long decoding")
 
 
-def test_a_large_sink_shows_in_the_logits(model_root, tmp_path):
-    """The sinks of a model are raised until they take most of every head's weight: the engine follows the plain model."""
+@pytest.mark.parametrize("name,dtype", [("Q", "float32"), ("U", "bfloat16"), ("T", "bfloat16")])
+def test_a_large_sink_shows_in_the_logits(model_root, tmp_path, name, dtype):
+    """The sinks of a model are raised until they take most of every head's weight: the engine follows the plain model
+    (in bfloat16 through the tensor-core kernels: tcgen05 for the prompt at key rows of 64, mma.sync else)."""
     torch = _torch()
     from machserve_b200.config import load_config
     from machserve_b200.engine.runner import ModelRunner, StepEntry
     from machserve_b200.parts import DecoderModel
     from machserve_b200.weights import load_weights
 
-    d = make_model_dir(model_root, "Q")
+    d = make_model_dir(model_root, name)
     config = load_config(d)
     tensors = load_weights(d, DecoderModel(config.model_spec()).tensors(), torch.float32, "cpu")
-    cfg, w = read_weights(d)
-    toks = random_tokens(cfg["vocab"], 40, 3)
+    cfg, w = read_weights(d, round_to_bf16=(dtype == "bfloat16"))
+    toks = random_tokens(cfg["vocab"], 150, 3)
     before = plain.forward(cfg, w, toks)
     for name in tensors:
         if name.endswith("mix.sink"):
@@ -458,9 +460,12 @@ def test_a_large_sink_shows_in_the_logits(model_root, tmp_path):
             w[name] = w[name] + 4.0
     after = plain.forward(cfg, w, toks)
     assert np.abs(after - before).max() > 0.05, "the test's sinks matter"
-    runner = ModelRunner(config, tensors, dtype="float32", page_size=16, num_pages=8, max_requests=2, max_step_tokens=64)
-    got = runner.step([StepEntry("a", toks, list(range(len(toks))))]).cpu().numpy()
-    assert_close(got, after, F32_TOL, "large sinks")
+    runner = ModelRunner(config, tensors, dtype=dtype, page_size=16, num_pages=16, max_requests=2, max_step_tokens=256)
+    got = runner.step([StepEntry("a", toks[:140], list(range(140)))]).cpu().numpy()
+    assert_close(got, after[:140], _tol(dtype), "large sinks, the prompt")
+    for p in range(140, 150):  # and decoded rows
+        got = runner.step([StepEntry("a", [toks[p]], [0])]).cpu().numpy()
+        assert_close(got[0], after[p], _tol(dtype), f"large sinks, decoded token {p}")
 
 
 @pytest.mark.parametrize("name,dtype", [("P", "float32"), ("S", "float32"), ("Q", "bfloat16")])

@@ -95,6 +95,19 @@ CASES = {
         },
         seed=15, page=16,
     ),
+    # key and value rows of 64 in an attention layer: the sizes at which the bfloat16 engine sends the portions of prompts
+    # to its tcgen05 attention (with the sink) and decoding rows to the mma.sync kernel
+    "U": dict(
+        config={
+            "architecture": "Venarax", "vocab": 192, "width": 128, "norm": {"eps": 1e-6},
+            "layers": [
+                {**_attention(4, 2, 64, 64, 0.125, 0.4, 10), "mlp": _mlp(160, 2.0)},
+                {**_latent(2, 32, 16, 32, 48, 0.15, 10000.0, 16, 70), "mlp": _mlp(96, 2.0)},
+            ],
+            "loop": {"start": 0, "stop": 1, "times": 2},
+        },
+        seed=16, page=16,
+    ),
 }
 
 
