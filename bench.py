@@ -576,6 +576,7 @@ def time_venarax_kernels(torch, ops, raw, pk):
         pairs = n * (n + 1) // 2 if not window else sum(min(p + 1, window) for p in range(n))
         flops = 2 * pairs * hq * (dk + dv)
         if vw and ops.attention_prefill_tc_supports(hd, page):
+            # at key and value rows of 64 or 128 the engine sends portions to the tcgen05 kernel, with the sink in its finish
             qp16, op16 = qp.to(bf), torch.empty(n, hq * hd, dtype=bf, device=dev)
             t0 = torch.arange(0, n, 128, dtype=torch.int32, device=dev)
             tn = torch.full_like(t0, 128)
@@ -584,9 +585,11 @@ def time_venarax_kernels(torch, ops, raw, pk):
             words = ops.attention_prefill_tc_scratch_words(tiles, hq, hd, splits_p)
             scr = torch.zeros(max(words, 1), dtype=torch.float32, device=dev) if words else None
             counters = torch.zeros(tiles * hq, dtype=torch.int32, device=dev) if words else None
-            t_like = us(lambda: ops.attention_prefill_tc(qp16, kp, vp, op16, t0, tn, tiles, posp, slotp, table, hq, hkv, hd, None, 0.1,
-                                                         splits_p, scr, counters, alone=alone, run_tiles=run_tiles), reps=2)
-            entry(name + "_prefill", t_new, t_like, flops=flops, like="attention_prefill_tc (tcgen05)")
+            tc = lambda sinks_: ops.attention_prefill_tc(qp16, kp, vp, op16, t0, tn, tiles, posp, slotp, table, hq, hkv, hd, None, 0.1,
+                                                         splits_p, scr, counters, alone=alone, run_tiles=run_tiles, sinks=sinks_)
+            t_sink, t_like = us(lambda: tc(sk), reps=2), us(lambda: tc(None), reps=2)
+            entry(name + "_prefill", t_sink, t_like, flops=flops, like="attention_prefill_tc (tcgen05) without a sink")
+            out[name + "_prefill"]["mma_kernel_us"] = round(t_new, 1)  # (what other widths get)
         else:
             entry(name + "_prefill", t_new, t_new, flops=flops, like="(no like kernel)")
         out[name + "_prefill"]["exact_kernel_us"] = round(t_exact, 1)

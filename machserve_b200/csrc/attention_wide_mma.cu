@@ -332,7 +332,7 @@ __global__ void __launch_bounds__(128)
 attention_wide_mma_merge_kernel(const float* __restrict__ scratch, __nv_bfloat16* __restrict__ out,
                                 const float* __restrict__ sinks, const int* __restrict__ slots,
                                 const int* __restrict__ unit_row0, int hq, int hkv, int dv, int dvp, int splits) {
-  __shared__ float w_s[32];
+  __shared__ float w_s[36];  // (four zeros behind the 32: the sums below go four splits at a time)
   ms_pdl_trigger();
   ms_pdl_wait();
   const int groups = hq / hkv;
@@ -359,11 +359,18 @@ attention_wide_mma_merge_kernel(const float* __restrict__ scratch, __nv_bfloat16
     for (int i = 0; i < splits; ++i) total += __shfl_sync(0xffffffffu, sum, i);
     if (sinks) total += ms_exp2(s2 - top);
     w_s[sp] = total > 0.f ? w / total : 0.f;
+    if (sp < 4) w_s[32 + sp] = 0.f;
   }
   __syncthreads();
   for (int d = threadIdx.x; d < dv; d += blockDim.x) {
     float acc = 0.f;
-    for (int sp = 0; sp < splits; ++sp) acc += w_s[sp] * base[sp * step + d];
+    for (int sp = 0; sp < splits; sp += 4) {  // four loads in flight; added in split order
+      float v[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) v[u] = sp + u < splits ? base[(sp + u) * step + d] : 0.f;
+#pragma unroll
+      for (int u = 0; u < 4; ++u) acc += w_s[sp + u] * v[u];
+    }
     out[((size_t)token * hq + head) * dv + d] = __float2bfloat16_rn(acc);
   }
 }
