@@ -36,7 +36,7 @@ def _dev(a, dtype=None):
 # ----------------------------------------------------------------------------------- mechanisms, one kernel each
 
 
-@pytest.mark.parametrize("d", [24, 64, 200, 1000])
+@pytest.mark.parametrize("d", [24, 50, 64, 200, 1000, 1531])
 def test_layer_norm_adds_two_deltas_and_writes_two_norms(d):
     torch = _torch()
     from machserve_b200 import ops
@@ -222,6 +222,48 @@ def test_tensor_core_attention_with_sink_and_unequal_widths(dk, dv, hq, hkv, win
     exact = torch.zeros(len(rows), hq * dv, dtype=bf, device="cuda")
     ops.attention_wide(_dev(q).view(len(rows), hq * dk), kd, vd, exact, sk, pos, slot, _dev(table), hq, hkv, dk, dv, window, scale, share_rows=True)
     assert_close(out.float().cpu().numpy(), exact.float().cpu().numpy(), 2e-2, "tensor-core form against the exact kernel")
+
+
+@pytest.mark.parametrize("hd,hq,hkv,n,splits", [(64, 4, 2, 300, 1), (64, 6, 1, 700, 3), (128, 4, 2, 300, 1), (128, 6, 2, 700, 2),
+                                                  (128, 3, 1, 520, 4)])
+def test_sink_in_the_tcgen05_attention(hd, hq, hkv, n, splits):
+    """The framework's tcgen05 attention for prompt portions with a sink per head in its finish: one head a block (head
+    size 64) and two heads of a group a block (128), whole and with the key tiles cut into runs that are merged; against
+    the exact kernel with the same sinks, and without sinks against itself as it was."""
+    torch = _torch()
+    from machserve_b200 import ops
+
+    rng = np.random.default_rng(hd + n)
+    bf, page = torch.bfloat16, 16
+    kp, table = _paged(rng, [n], hkv, hd, page, "bfloat16")
+    vp = np.zeros_like(kp)
+    _fill_pages(kp, table, 0, rng.normal(size=(n, hkv, hd)).astype(np.float32), page)
+    _fill_pages(vp, table, 0, rng.normal(size=(n, hkv, hd)).astype(np.float32), page)
+    kd, vd = _dev(kp, bf), _dev(vp, bf)
+    q = _dev(rng.normal(size=(n, hq * hd)).astype(np.float32), bf)
+    sinks = _dev((rng.normal(size=hq) * 2 + 1).astype(np.float32))
+    pos = torch.arange(n, dtype=torch.int32, device="cuda")
+    slot = torch.zeros(n, dtype=torch.int32, device="cuda")
+    t0 = torch.arange(0, n, 128, dtype=torch.int32, device="cuda")
+    tn = torch.tensor([min(128, n - a) for a in range(0, n, 128)], dtype=torch.int32, device="cuda")
+    tiles, scale = t0.numel(), hd ** -0.5
+    scratch = counters = None
+    if splits > 1:
+        scratch = torch.zeros(ops.attention_prefill_tc_scratch_words(tiles, hq, hd, splits), device="cuda")
+        counters = torch.zeros(tiles * hq, dtype=torch.int32, device="cuda")
+    outs = {}
+    for name, sk in (("sinks", sinks), ("plain", None)):
+        out = torch.zeros(n, hq * hd, dtype=bf, device="cuda")
+        ops.attention_prefill_tc(q, kd, vd, out, t0, tn, tiles, pos, slot, _dev(table), hq, hkv, hd, None, scale, splits, scratch, counters,
+                                 sinks=sk)
+        exact = torch.zeros(n, hq * hd, dtype=bf, device="cuda")
+        ops.attention_wide(q.float(), kd, vd, exact, sk, pos, slot, _dev(table), hq, hkv, hd, hd, None, scale, share_rows=True)
+        assert_close(out.float().cpu().numpy(), exact.float().cpu().numpy(), 2e-2, f"tcgen05 attention, {name}, {splits} runs")
+        outs[name] = out.float().cpu().numpy()
+    assert ops.tc_status_codes() == (0, 0)
+    if counters is not None:
+        assert int(counters.abs().sum()) == 0, "the counters are left zero"
+    assert np.abs(outs["sinks"] - outs["plain"]).max() > 0.05, "the test's sinks matter"
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
