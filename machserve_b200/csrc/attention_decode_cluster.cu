@@ -38,3 +38,16 @@ MS_API int ms_attention_decode_cluster(const void* q, const void* k_pages, const
                                  slot_of_token, block_table, max_pages, num_pages, tokens, hq, hkv, hd, page_size, window,
                                  scale, num_splits, stages, warps, keys_per_warp, parts, scratch, scratch_words, counters, num_counters, stream);
 }
+
+// The same with a sink per query head: sinks float32 [hq]; exp(sink) joins the softmax's denominator and has no value.
+MS_API int ms_attention_decode_cluster_sinks(const void* q, const void* k_pages, const void* v_pages, void* out,
+                                             const int* rows, const int* positions, const int* slot_of_token,
+                                             const int* block_table, int max_pages, int num_pages, int tokens, int hq, int hkv,
+                                             int hd, int page_size, int window, float scale, int num_splits, int stages,
+                                             int warps, int keys_per_warp, int parts, float* scratch, long long scratch_words,
+                                             int* counters, int num_counters, const float* sinks, cudaStream_t stream) {
+  return decode_cluster_dispatch<false>(q, nullptr, const_cast<void*>(k_pages), const_cast<void*>(v_pages), out, rows, positions,
+                                 slot_of_token, block_table, max_pages, num_pages, tokens, hq, hkv, hd, page_size, window,
+                                 scale, num_splits, stages, warps, keys_per_warp, parts, scratch, scratch_words, counters, num_counters, stream,
+                                 sinks);
+}

@@ -45,7 +45,19 @@ struct DclOuter {
   int parts;  // 1: the cluster writes the output itself
   float* scratch;
   int* counters;
+  const float* sinks;  // [hq] or null: exp(sink) of a row's head joins its softmax's denominator and has no value
 };
+
+// The sink joins a row's finished sums (m and l in the log2 domain, o the row's coordinate): against the reference m,
+// or as the reference if it is larger.
+__device__ __forceinline__ void dcl_add_sink(const float* __restrict__ sinks, int head, float m, float& l, float& f) {
+  f = 1.f;
+  if (sinks == nullptr) return;
+  const float s2 = sinks[head] * MS_LOG2E;
+  const float top = fmaxf(m, s2);
+  f = ms_exp2(m - top);
+  l = l * f + ms_exp2(s2 - top);
+}
 #define DCL_MAX_PARTS 16
 
 // Requests `ntiles` tiles of 64 keys and their values, starting at tile `tile0`, into consecutive stages.  One
@@ -408,6 +420,9 @@ attention_decode_cluster_kernel(const __nv_bfloat16* __restrict__ q, DclRaw raw,
     }
     if (num_splits == 1) {
       if (live) {
+        float fs;
+        dcl_add_sink(outer.sinks, kvh * groups + r, m, l, fs);
+        o.x *= fs; o.y *= fs; o.z *= fs; o.w *= fs;
         __nv_bfloat16* dst = out + ((size_t)t * hq + kvh * groups + r) * HD + d;
         *reinterpret_cast<uint2*>(dst) = make_uint2(ms_pack_bf16(l > 0.f ? __fdividef(o.x, l) : 0.f, l > 0.f ? __fdividef(o.y, l) : 0.f),
                                                     ms_pack_bf16(l > 0.f ? __fdividef(o.z, l) : 0.f, l > 0.f ? __fdividef(o.w, l) : 0.f));
@@ -457,6 +472,9 @@ attention_decode_cluster_kernel(const __nv_bfloat16* __restrict__ q, DclRaw raw,
           __stcg(mine + total + 16 + r, l);
         }
       } else if (live) {
+        float fs;
+        dcl_add_sink(outer.sinks, kvh * groups + r, m, l, fs);
+        o *= fs;
         out[((size_t)t * hq + kvh * groups + r) * HD + d] = __float2bfloat16_rn(l > 0.f ? __fdividef(o, l) : 0.f);
       }
     }
@@ -491,7 +509,12 @@ attention_decode_cluster_kernel(const __nv_bfloat16* __restrict__ q, DclRaw raw,
       l += __ldcg(pk + total + 16 + r) * f;
       o += __ldcg(pk + e) * f;
     }
-    if (live) out[((size_t)t * hq + kvh * groups + r) * HD + (e - r * HD)] = __float2bfloat16_rn(l > 0.f ? __fdividef(o, l) : 0.f);
+    if (live) {
+      float fs;
+      dcl_add_sink(outer.sinks, kvh * groups + r, m, l, fs);
+      o *= fs;
+      out[((size_t)t * hq + kvh * groups + r) * HD + (e - r * HD)] = __float2bfloat16_rn(l > 0.f ? __fdividef(o, l) : 0.f);
+    }
   }
   if (tid == 0) *counter = 0;
 }
@@ -595,7 +618,7 @@ static int decode_cluster_dispatch(const void* q, const DclRaw* raw, void* k_pag
                                    const int* block_table, int max_pages, int num_pages, int tokens, int hq, int hkv,
                                    int hd, int page_size, int window, float scale, int num_splits, int stages,
                                    int warps, int kpw, int parts, float* scratch, long long scratch_words, int* counters,
-                                   int num_counters, cudaStream_t stream) {
+                                   int num_counters, cudaStream_t stream, const float* sinks = nullptr) {
   if (tokens == 0) return 0;
   MS_REQUIRE(parts >= 1 && parts <= DCL_MAX_PARTS, "attention_decode_cluster: %d clusters a pair; 1 to %d", parts, DCL_MAX_PARTS);
   if (parts > 1) {
@@ -606,7 +629,7 @@ static int decode_cluster_dispatch(const void* q, const DclRaw* raw, void* k_pag
                "attention_decode_cluster: %d clusters a pair need %lld words of scratch and %d counters; %lld and %d were given",
                parts, need, tokens * hkv, scratch ? scratch_words : 0LL, counters ? num_counters : 0);
   }
-  const DclOuter outer = {parts, scratch, counters};
+  const DclOuter outer = {parts, scratch, counters, sinks};
   MS_REQUIRE(warps == 4 || warps == 8, "attention_decode_cluster: 4 or 8 warps a block, not %d", warps);
   MS_REQUIRE(kpw == 0 || kpw == 16 || kpw == 32 || kpw == 64, "attention_decode_cluster: a warp takes 16, 32 or 64 keys at a time (0: by rule), not %d", kpw);
   MS_REQUIRE(tokens > 0 && hq > 0 && hkv > 0 && hq % hkv == 0 && hkv <= 65535, "attention_decode_cluster: bad head counts hq=%d hkv=%d", hq, hkv);

@@ -83,6 +83,7 @@ class _Signatures:
     ms_attention_decode = [P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, I, P]
     ms_gemm_small_m_plan = [I, I, I, I, I, I, P]
     ms_attention_decode_cluster = [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, I, I, I, I, I, P, LL, P, I, P]
+    ms_attention_decode_cluster_sinks = [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, I, I, I, I, I, P, LL, P, I, P, P]
     ms_attention_decode_cluster_rope = [P, I, P, P, I, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, I, I, I, I, I, P, LL, P, I, P]
     ms_attention_prefill_tc = [P, P, P, P, I, P, P, I, P, P, P, I, I, I, I, I, I, I, F, I, I, I, P, LL, P, LL, P]
     ms_attention_prefill_tc_plan = [I, I, I, I, I, I, I, P]
@@ -396,13 +397,15 @@ def _outer_args(name, tokens, num_heads, num_kv_heads, head_dim, parts, scratch,
 
 def attention_decode_cluster(q, k_pages, v_pages, out, positions, slot_of_token, block_table, num_heads, num_kv_heads,
                              head_dim, window, scale, num_splits, stages, rows=None, num_rows=None, warps=4, keys_per_warp=0,
-                             parts=1, scratch=None, counters=None):
+                             parts=1, scratch=None, counters=None, sinks=None):
     """As attention_decode, with the splits of a row held by one thread-block cluster (1, 2, 4 or 8) and merged in
     shared memory: no scratch.  Keys and values of earlier positions are requested before the kernel waits for its
     predecessor in the stream.  `stages`: tiles of 64 keys a block holds at once.  `parts` > 1 (few rows with long
     contexts): a row's keys go to that many clusters, which leave their sums in `scratch`; the one that ends last
-    merges them in order (`counters`: int32 zeros, left zero)."""
+    merges them in order (`counters`: int32 zeros, left zero).  `sinks` (float32, one per head): exp(sink) joins every
+    row's softmax denominator and has no value."""
     tokens = q.shape[0] if rows is None else int(num_rows)
+    _need(sinks is None or (sinks.dtype == torch.float32 and sinks.numel() == num_heads), "attention_decode_cluster: bad sinks")
     outer = _outer_args("attention_decode_cluster", tokens, num_heads, num_kv_heads, head_dim, parts, scratch, counters)
     _need(rows is None or (rows.dtype == torch.int32 and rows.numel() >= tokens), "attention_decode_cluster: bad row list")
     _need(q.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and k_pages.dtype == torch.bfloat16,
@@ -412,10 +415,11 @@ def attention_decode_cluster(q, k_pages, v_pages, out, positions, slot_of_token,
     _need(tuple(k_pages.shape[1:]) == (num_kv_heads, k_pages.shape[2], head_dim), "attention_decode_cluster: bad page shape")
     _need(block_table.dtype == torch.int32 and block_table.is_contiguous(), "attention_decode_cluster: bad block table")
     _check(
-        lib().ms_attention_decode_cluster(
+        lib().ms_attention_decode_cluster_sinks(
             _ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(out), _ptr(rows), _ptr(positions), _ptr(slot_of_token),
             _ptr(block_table), block_table.shape[1], k_pages.shape[0], tokens, num_heads, num_kv_heads, head_dim,
-            k_pages.shape[2], int(window or 0), float(scale), int(num_splits), int(stages), int(warps), int(keys_per_warp), *outer, _stream(),
+            k_pages.shape[2], int(window or 0), float(scale), int(num_splits), int(stages), int(warps), int(keys_per_warp), *outer,
+            _ptr(sinks), _stream(),
         ),
         "attention_decode_cluster",
     )

@@ -8,6 +8,61 @@ from ..weights.loader import TensorDecl
 from .base import POSITION_ENCODINGS, Mixer, PagedKV, RowStats, WorkPlan, as_delta, matrix, register_mixer, vector_f32
 
 
+def decode_launch(rt, hd: int, max_stages: int, cache: dict, units: int, tiles: int):
+    """(splits, stages, warps, keys per warp, clusters per pair) for `units` (row, kv head) pairs whose longest run of keys has `tiles`
+    tiles of 64.  What the measurements on B200 (head sizes 64 and 128, 8 to 64 rows, 1,000 to 2,048 keys) come to:
+    all blocks of the launch are resident at once (a second wave costs more than fewer, longer blocks), as many
+    splits as that allows up to three and a half blocks per SM, never more blocks than half the tiles.  A block
+    holds its whole run of tiles when that fits (all of it is requested before the wait for the preceding
+    kernel); else it goes through the run with a ring of four or two stages (more blocks on an SM hide the
+    latency of a row's chain of steps better than a deeper ring does), or, when the run is short, a tile at a time."""
+    key = (units, tiles)
+    hit = cache.get(key)
+    if hit is not None:
+        return hit
+    sm = rt.sm_count
+    choice = None
+    for splits in (8, 4, 2, 1):
+        if splits > 1 and (2 * splits > tiles or splits * units > 3.5 * sm):
+            continue
+        blocks, per = splits * units, -(-tiles // splits)
+        ring = [n for n in (4, 2, 1) if n < per and n <= max_stages and (n <= 2 or hd <= 64) and (n > 1 or per <= 4)]
+        for stages in ([per] if per <= max_stages else []) + ring:
+            if blocks <= sm * ops.attention_decode_cluster_blocks_per_sm(hd, stages):
+                choice = (splits, stages, per)
+                break
+        if choice:
+            break
+    splits, stages, per = choice or (1, min(2, max_stages, tiles), tiles)
+    # Few rows with long contexts leave most SMs without a block: a pair's keys then go to `parts` clusters, whose
+    # sums meet in scratch memory (about 4 us more).  Measured (1 to 8 rows, 8,192 and 32,768 keys, both head sizes):
+    # worth it while the launch stays at one block per SM and a block keeps four tiles, or, for long runs, at two
+    # blocks per SM and 32 tiles (inside a step, a second block per SM delays the kernels that follow, which
+    # start early to request their weights: batch 8 at 16,384 keys lost 4 % with runs of 16 tiles).
+    parts = 1
+    while splits == 8 and parts < 16 and hd in (64, 128):  # (the head sizes the kernel has this form for)
+        blocks, run = 8 * units * 2 * parts, tiles // (8 * 2 * parts)
+        if not ((blocks <= 2 * sm and run >= 32) or (8 * units <= sm // 4 and blocks <= sm and run >= 4)):
+            break
+        parts *= 2
+    if parts > 1:
+        per = -(-tiles // (8 * parts))
+        stages = min(per, max_stages)
+        warps = 8 if hd <= 64 else 4
+        cache[key] = (splits, stages, warps, 0, parts)
+        return cache[key]
+    blocks = splits * units
+    # head sizes up to 64 with four or more tiles at once: eight warps, with half a tile each when the block holds its
+    # whole run, with a quarter each when it goes through a ring (of two places of two tiles); else four warps, and a
+    # quarter of a tile each in a ring.  (Eight warps were first kept to launches of one block per SM; with more
+    # blocks they change nothing at 2,048 keys and win at longer runs: batch 64 at 8,192 keys 2.18 -> 2.09 ms a step.)
+    ring = 2 <= stages < per
+    warps = 8 if stages >= 4 and hd <= 64 else 4
+    kpw = 16 if ring else 0
+    cache[key] = (splits, stages, warps, kpw, 1)
+    return cache[key]
+
+
 @register_mixer("attention")
 class Attention(Mixer):
     """q, k, v projections (+ bias), position encoding of q and k, write of k and v into the
@@ -232,58 +287,8 @@ class Attention(Mixer):
         return self.attend(ctx, self.encode_store(ctx, qkv, cache, store), cache, out)
 
     def _single_launch(self, units: int, tiles: int):
-        """(splits, stages, warps, keys per warp, clusters per pair) for `units` (row, kv head) pairs whose longest run of keys has `tiles`
-        tiles of 64.  What the measurements on B200 (head sizes 64 and 128, 8 to 64 rows, 1,000 to 2,048 keys) come to:
-        all blocks of the launch are resident at once (a second wave costs more than fewer, longer blocks), as many
-        splits as that allows up to three and a half blocks per SM, never more blocks than half the tiles.  A block
-        holds its whole run of tiles when that fits (all of it is requested before the wait for the preceding
-        kernel); else it goes through the run with a ring of four or two stages (more blocks on an SM hide the
-        latency of a row's chain of steps better than a deeper ring does), or, when the run is short, a tile at a time."""
-        key = (units, tiles)
-        hit = self._launch_cache.get(key)
-        if hit is not None:
-            return hit
-        sm, hd = self.rt.sm_count, self.hd
-        choice = None
-        for splits in (8, 4, 2, 1):
-            if splits > 1 and (2 * splits > tiles or splits * units > 3.5 * sm):
-                continue
-            blocks, per = splits * units, -(-tiles // splits)
-            ring = [n for n in (4, 2, 1) if n < per and n <= self.max_stages and (n <= 2 or hd <= 64) and (n > 1 or per <= 4)]
-            for stages in ([per] if per <= self.max_stages else []) + ring:
-                if blocks <= sm * ops.attention_decode_cluster_blocks_per_sm(hd, stages):
-                    choice = (splits, stages, per)
-                    break
-            if choice:
-                break
-        splits, stages, per = choice or (1, min(2, self.max_stages, tiles), tiles)
-        # Few rows with long contexts leave most SMs without a block: a pair's keys then go to `parts` clusters, whose
-        # sums meet in scratch memory (about 4 us more).  Measured (1 to 8 rows, 8,192 and 32,768 keys, both head sizes):
-        # worth it while the launch stays at one block per SM and a block keeps four tiles, or, for long runs, at two
-        # blocks per SM and 32 tiles (inside a step, a second block per SM delays the kernels that follow, which
-        # start early to request their weights: batch 8 at 16,384 keys lost 4 % with runs of 16 tiles).
-        parts = 1
-        while splits == 8 and parts < 16 and hd in (64, 128):  # (the head sizes the kernel has this form for)
-            blocks, run = 8 * units * 2 * parts, tiles // (8 * 2 * parts)
-            if not ((blocks <= 2 * sm and run >= 32) or (8 * units <= sm // 4 and blocks <= sm and run >= 4)):
-                break
-            parts *= 2
-        if parts > 1:
-            per = -(-tiles // (8 * parts))
-            stages = min(per, self.max_stages)
-            warps = 8 if hd <= 64 else 4
-            self._launch_cache[key] = (splits, stages, warps, 0, parts)
-            return self._launch_cache[key]
-        blocks = splits * units
-        # head sizes up to 64 with four or more tiles at once: eight warps, with half a tile each when the block holds its
-        # whole run, with a quarter each when it goes through a ring (of two places of two tiles); else four warps, and a
-        # quarter of a tile each in a ring.  (Eight warps were first kept to launches of one block per SM; with more
-        # blocks they change nothing at 2,048 keys and win at longer runs: batch 64 at 8,192 keys 2.18 -> 2.09 ms a step.)
-        ring = 2 <= stages < per
-        warps = 8 if stages >= 4 and hd <= 64 else 4
-        kpw = 16 if ring else 0
-        self._launch_cache[key] = (splits, stages, warps, kpw, 1)
-        return self._launch_cache[key]
+        """The launch of the decode kernel for this part's head size (`decode_launch`)."""
+        return decode_launch(self.rt, self.hd, self.max_stages, self._launch_cache, units, tiles)
 
     def _attend_single(self, ctx, q, cache, out, raw=None):
         """Rows that are alone in their sequences: a cluster of blocks per (row, kv head)."""

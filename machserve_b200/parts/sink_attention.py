@@ -67,6 +67,8 @@ class SinkAttention(wide_attend.WideAttendPlan, Mixer):
         self.q_norm, self.k_norm = vector_f32(tensors[p + "q.norm"]), vector_f32(tensors[p + "k.norm"])
         self.sinks = vector_f32(tensors[p + "sink"]) if self.has_sink else None
         self.fast = wide_attend.supports(rt, self.dk, self.dv, self.dv, True)  # bfloat16: the tensor-core kernel
+        # keys and values of one width that the framework's decode kernel is built for: decoding rows go there
+        self.cluster = {} if self.fast and wide_attend.cluster_covers(rt, self.dk, self.dv, self.hq // self.hkv) else None
 
     def forward(self, ctx, x, cache, owns_cache=True):
         rt, t = self.rt, x.shape[0]
@@ -77,14 +79,14 @@ class SinkAttention(wide_attend.WideAttendPlan, Mixer):
         q = ws.get("sink_attn.q", (t, self.qw), torch.float32)
         k_pages, v_pages = cache.planes["k"], cache.planes["v"]
         table = cache.block_table(ctx)
-        # a step with portions of prompts: their rows go to the tcgen05 kernel where it covers the sizes; it reads bfloat16 queries
-        q_half = None
-        if self.fast and ctx.max_query_len > 1 and wide_attend.tcgen05_covers(rt, self.dk, self.dv, k_pages.shape[2]):
-            q_half = ws.get("sink_attn.q_half", (t, self.qw), rt.dtype)
+        # the framework's kernels for keys and values of one width read bfloat16 queries: portions of prompts go to the tcgen05
+        # kernel where it covers the sizes, decoding rows to the cluster kernel
+        tcgen05 = self.fast and ctx.max_query_len > 1 and wide_attend.tcgen05_covers(rt, self.dk, self.dv, k_pages.shape[2])
+        q_half = ws.get("sink_attn.q_half", (t, self.qw), rt.dtype) if tcgen05 or self.cluster is not None else None
         ops.qk_norm_store(proj, self.q_norm, self.k_norm, self.eps, self.coef, self.every, ctx.positions, ctx.slot_of_token, table,
                           q, k_pages, v_pages, self.hkv, self.dk, self.dv, store=owns_cache, q_half=q_half)
         out = ws.get("sink_attn.out", (t, self.hq * self.dv), rt.dtype)
         wide_attend.attend(ctx, rt, self.fast, table, q, k_pages, v_pages, out, self.sinks, self.hq, self.hkv, self.dk, self.dv,
-                           self.window, self.scale, q_half=q_half)
+                           self.window, self.scale, q_half=q_half, tcgen05=tcgen05, cluster=self.cluster)
         delta = ws.get("mixer.delta_f32", (t, self.hidden), torch.float32)
         return ops.linear(out, self.w_o, None, delta)

@@ -89,17 +89,50 @@ def attend_portions_tcgen05(ctx, rt, table, q_half, k_pages, v_pages, out, sinks
                                     alone=alone, run_tiles=run_tiles, sinks=sinks)
 
 
+def cluster_covers(rt, dk: int, dv: int, groups: int) -> bool:
+    """Whether decoding rows can go to the framework's cluster kernel: keys and values of one width that it is built for."""
+    return rt.dtype == torch.bfloat16 and dk == dv and ops.attention_decode_supports(dk, groups) and ops.attention_prefill_supports(dk)
+
+
+def attend_single_cluster(ctx, rt, launch_cache: dict, table, q_half, k_pages, v_pages, out, sinks, hq: int, hkv: int, hd: int, window,
+                          scale: float):
+    """Rows that are alone in their sequences on the framework's decode kernel (a cluster of blocks per row and key head,
+    the launch by the rules measured for it), with the sink in its merge."""
+    from .attention import decode_launch
+
+    work = ctx.work[PLAN]
+    t = work.sizes["single_rows"]
+    tiles = (work.shape[0] * CONTEXT_BUCKET + 63) // 64
+    if window:
+        tiles = min(tiles, (window + 63) // 64 + 1)
+    splits, stages, warps, kpw, parts = decode_launch(rt, hd, ops.attention_decode_cluster_max_stages(hd), launch_cache, t * hkv, tiles)
+    scratch = counters = None
+    if parts > 1:
+        words = ops.attention_decode_cluster_scratch_words(t, hq, hkv, hd, parts)
+        scratch = rt.workspace.get("wide_attend.decode_parts", (words,), torch.float32)
+        counters = rt.workspace.get("wide_attend.decode_counters", (t * hkv,), torch.int32, zero=True)
+    every_row = work.sizes["tile128_row0"] == 0 and t == q_half.shape[0]
+    return ops.attention_decode_cluster(q_half, k_pages, v_pages, out, ctx.positions, ctx.slot_of_token, table, hq, hkv, hd, window, scale,
+                                        splits, stages, rows=None if every_row else work.lists["single_rows"], num_rows=t, warps=warps,
+                                        keys_per_warp=kpw, parts=parts, scratch=scratch, counters=counters, sinks=sinks)
+
+
 def attend(ctx, rt, fast: bool, table, q, k_pages, v_pages, out, sinks, hq: int, hkv: int, dk: int, dv: int, window, scale: float,
-           q_half=None):
+           q_half=None, tcgen05: bool = False, cluster=None):
     """Every row of q over its sequence's pages: on the tensor cores when the widths allow it in bfloat16 (decoding rows
-    with their key tiles cut into as many runs as fill the GPU, portions in tiles of 64, 32 or 16 rows), else the exact kernel."""
+    with their key tiles cut into as many runs as fill the GPU, portions in tiles of 64, 32 or 16 rows), else the exact kernel.
+    With `q_half` (the queries in bfloat16) the framework's own kernels for keys and values of one width take what they
+    cover: `cluster` (a dict for the launch rules' results) sends decoding rows to its cluster kernel, `tcgen05` the
+    portions to its tcgen05 kernel; both add the sinks themselves."""
     if not fast:
         return ops.attention_wide(q, k_pages, v_pages, out, sinks, ctx.positions, ctx.slot_of_token, table, hq, hkv,
                                   dk, dv, window, scale, share_rows=ctx.max_query_len > 1)
     work = ctx.work[PLAN]
     tile = ops.attention_wide_mma_tile_rows(dv)
     singles, tiles = work.sizes["single_rows"], work.sizes[f"tile{tile}_row0"]
-    if singles:
+    if singles and cluster is not None and q_half is not None:
+        attend_single_cluster(ctx, rt, cluster, table, q_half, k_pages, v_pages, out, sinks, hq, hkv, dk, window, scale)
+    elif singles:
         items = singles * hkv * (-(-(hq // hkv) // 16))
         keys = work.shape[0] * CONTEXT_BUCKET
         if window:
@@ -111,7 +144,7 @@ def attend(ctx, rt, fast: bool, table, q, k_pages, v_pages, out, sinks, hq: int,
         rows = None if tiles == 0 and singles == q.shape[0] else work.lists["single_rows"]
         ops.attention_wide_mma(q, k_pages, v_pages, out, sinks, ctx.positions, ctx.slot_of_token, table, rows, None, singles, True,
                                hq, hkv, dk, dv, window, scale, splits, scratch)
-    if q_half is not None:  # portions on the tcgen05 kernel (the part has made sure that it covers the sizes)
+    if tcgen05 and q_half is not None:  # portions on the tcgen05 kernel (the part has made sure that it covers the sizes)
         attend_portions_tcgen05(ctx, rt, table, q_half, k_pages, v_pages, out, sinks, hq, hkv, dk, window, scale)
     elif tiles:
         ops.attention_wide_mma(q, k_pages, v_pages, out, sinks, ctx.positions, ctx.slot_of_token, table, work.lists[f"tile{tile}_row0"],

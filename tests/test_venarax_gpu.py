@@ -241,7 +241,7 @@ def test_sink_in_the_tcgen05_attention(hd, hq, hkv, n, splits):
     _fill_pages(vp, table, 0, rng.normal(size=(n, hkv, hd)).astype(np.float32), page)
     kd, vd = _dev(kp, bf), _dev(vp, bf)
     q = _dev(rng.normal(size=(n, hq * hd)).astype(np.float32), bf)
-    sinks = _dev((rng.normal(size=hq) * 2 + 1).astype(np.float32))
+    sinks = _dev((rng.normal(size=hq) + np.log(n / 2)).astype(np.float32))  # about half of a middle row's weight
     pos = torch.arange(n, dtype=torch.int32, device="cuda")
     slot = torch.zeros(n, dtype=torch.int32, device="cuda")
     t0 = torch.arange(0, n, 128, dtype=torch.int32, device="cuda")
@@ -264,6 +264,49 @@ def test_sink_in_the_tcgen05_attention(hd, hq, hkv, n, splits):
     if counters is not None:
         assert int(counters.abs().sum()) == 0, "the counters are left zero"
     assert np.abs(outs["sinks"] - outs["plain"]).max() > 0.05, "the test's sinks matter"
+
+
+@pytest.mark.parametrize("hd,hq,hkv,rows,ctx", [(64, 4, 2, 5, 300), (96, 4, 2, 8, 1100), (128, 8, 2, 3, 700), (64, 14, 2, 2, 9000),
+                                                  (128, 4, 1, 1, 6000), (32, 6, 3, 20, 150)])
+def test_sink_in_the_cluster_decode_attention(hd, hq, hkv, rows, ctx):
+    """The framework's decode kernel (clusters of blocks over a row's keys, several clusters a row for few rows with long
+    contexts) with a sink per head in its merges, launched by its own rules; against the exact kernel with the same sinks."""
+    torch = _torch()
+    from types import SimpleNamespace
+
+    from machserve_b200 import ops
+    from machserve_b200.parts.attention import decode_launch
+
+    rng = np.random.default_rng(hd + ctx)
+    bf, page = torch.bfloat16, 16
+    lens = [ctx - 7 * i for i in range(rows)]
+    kp, table = _paged(rng, lens, hkv, hd, page, "bfloat16")
+    kd = _dev(rng.normal(size=kp.shape).astype(np.float32), bf)
+    vd = _dev(rng.normal(size=kp.shape).astype(np.float32), bf)
+    q = _dev(rng.normal(size=(rows, hq * hd)).astype(np.float32), bf)
+    sinks = _dev((rng.normal(size=hq) + np.log(ctx)).astype(np.float32))  # about half of a row's weight
+    pos = torch.tensor([n - 1 for n in lens], dtype=torch.int32, device="cuda")
+    slot = torch.arange(rows, dtype=torch.int32, device="cuda")
+    scale = hd ** -0.5
+    rt = SimpleNamespace(sm_count=torch.cuda.get_device_properties(0).multi_processor_count)
+    splits, stages, warps, kpw, parts = decode_launch(rt, hd, ops.attention_decode_cluster_max_stages(hd), {}, rows * hkv, -(-ctx // 64))
+    scratch = counters = None
+    if parts > 1:
+        scratch = torch.zeros(ops.attention_decode_cluster_scratch_words(rows, hq, hkv, hd, parts), device="cuda")
+        counters = torch.zeros(rows * hkv, dtype=torch.int32, device="cuda")
+    outs = {}
+    for name, sk in (("sinks", sinks), ("plain", None)):
+        out = torch.zeros(rows, hq * hd, dtype=bf, device="cuda")
+        ops.attention_decode_cluster(q, kd, vd, out, pos, slot, _dev(table), hq, hkv, hd, None, scale, splits, stages, warps=warps,
+                                     keys_per_warp=kpw, parts=parts, scratch=scratch, counters=counters, sinks=sk)
+        exact = torch.zeros(rows, hq * hd, dtype=bf, device="cuda")
+        ops.attention_wide(q.float(), kd, vd, exact, sk, pos, slot, _dev(table), hq, hkv, hd, hd, None, scale)
+        assert_close(out.float().cpu().numpy(), exact.float().cpu().numpy(), 2e-2,
+                     f"cluster decode, {name}, {splits} splits, {parts} clusters a row")
+        outs[name] = out.float().cpu().numpy()
+    if (hd, rows) in ((64, 2), (128, 1)):
+        assert parts > 1, "the long contexts of few rows are meant to go to several clusters a row"
+    assert np.abs(outs["sinks"] - outs["plain"]).max() > 0.02, "the test's sinks matter"
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
