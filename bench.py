@@ -554,11 +554,19 @@ def time_venarax_kernels(torch, ops, raw, pk):
                                                   splits, scratch))
         t_exact = us(lambda: ops.attention_wide(q, kp, vp, o, sk, pos, slot, table, hq, h_kv, dk, dv, window, 0.1), reps=2)
         nbytes = b * seen * h_kv * (dk + (dv if vw else 0)) * 2
-        if vw:  # the dense decoder's decode kernel at the same sizes
+        if vw:  # keys and values of one width: the engine sends decoding rows to the cluster kernel, with the sink in its merges
+            from types import SimpleNamespace
+
+            from machserve_b200.parts.attention import decode_launch
+
             q16, o16 = q.to(bf), torch.empty(b, hq * hd, dtype=bf, device=dev)
-            t_like = us(lambda: ops.attention_decode_cluster(q16, kp, vp, o16, pos, slot, table, hq, hkv, hd, None, 0.1, 4,
-                                                             min(2, ops.attention_decode_cluster_max_stages(hd))))
-            entry(name + "_decode", t_new, t_like, nbytes, like="attention_decode_cluster (mma.sync, bfloat16)")
+            sp, stg, wr, kpw, parts = decode_launch(SimpleNamespace(sm_count=ops.sm_count()), hd, ops.attention_decode_cluster_max_stages(hd),
+                                                    {}, b * hkv, -(-ctx // 64))
+            cl = lambda sinks_: ops.attention_decode_cluster(q16, kp, vp, o16, pos, slot, table, hq, hkv, hd, None, 0.1, sp, stg, warps=wr,
+                                                             keys_per_warp=kpw, parts=1, sinks=sinks_)
+            t_sink, t_like = us(lambda: cl(sk)), us(lambda: cl(None))
+            entry(name + "_decode", t_sink, t_like, nbytes, like="attention_decode_cluster without a sink")
+            out[name + "_decode"]["mma_kernel_us"] = round(t_new, 1)  # (what other widths get)
         else:
             entry(name + "_decode", t_new, t_new, nbytes, like="(no like kernel: one plane read for keys and values)")
         out[name + "_decode"]["exact_kernel_us"] = round(t_exact, 1)

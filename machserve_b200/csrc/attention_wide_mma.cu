@@ -84,14 +84,6 @@ attention_wide_mma_kernel(const float* __restrict__ q, const __nv_bfloat16* __re
       lo[t][i] = (window > 0 && p - window + 1 > 0) ? p - window + 1 : 0;
     }
 
-  // Q: float32 rows -> bfloat16 tile (rows past `live` are zero)
-  for (int e = threadIdx.x; e < ROWS * dk; e += blockDim.x) {
-    const int r = e / dk, d = e - r * dk;
-    float v = 0.f;
-    if (r < live) v = HEADS ? q[((size_t)row0 * hq + head0 + r) * dk + d] : q[((size_t)(row0 + r) * hq + head0) * dk + d];
-    q_s[r * ks_stride + d] = __float2bfloat16_rn(v);
-  }
-
   float o[MT][DVW / 8][4];
   float m[MT][2], l[MT][2];
 #pragma unroll
@@ -131,8 +123,15 @@ attention_wide_mma_kernel(const float* __restrict__ q, const __nv_bfloat16* __re
     ms_cp_async_commit();
   };
 
+  if (first_tile + split <= last_tile) request(first_tile + split, 0);  // (on its way while the queries are brought in)
+  // Q: float32 rows -> bfloat16 tile (rows past `live` are zero)
+  for (int e = threadIdx.x; e < ROWS * dk; e += blockDim.x) {
+    const int r = e / dk, d = e - r * dk;
+    float v = 0.f;
+    if (r < live) v = HEADS ? q[((size_t)row0 * hq + head0 + r) * dk + d] : q[((size_t)(row0 + r) * hq + head0) * dk + d];
+    q_s[r * ks_stride + d] = __float2bfloat16_rn(v);
+  }
   __syncthreads();  // Q has been written
-  if (first_tile + split <= last_tile) request(first_tile + split, 0);
   int it = 0;
 #pragma unroll 1
   for (int tile = first_tile + split; tile <= last_tile; tile += splits, ++it) {
