@@ -867,15 +867,18 @@ def main() -> int:
         return time_gemm_pair_tc(torch, ops, a, pk)
     if a.kernel == "attention_prefill":
         return time_attention_prefill(torch, ops, a, pk)
+    other = False  # a model folder of another architecture than the dense decoder: bytes are taken from the runner itself
     if a.model:
         raw = json.load(open(os.path.join(a.model, "config.json")))
-        raw.setdefault("num_key_value_heads", raw["num_attention_heads"])
-        raw.setdefault("tie_word_embeddings", False)
+        other = "num_attention_heads" not in raw
+        if not other:
+            raw.setdefault("num_key_value_heads", raw["num_attention_heads"])
+            raw.setdefault("tie_word_embeddings", False)
         name = os.path.basename(os.path.normpath(a.model))
     else:
         raw, name = SHAPES[a.shape], {"qwen2.5-0.5b": "Qwen2.5-0.5B sizes", "qwen2.5-1.5b": "Qwen2.5-1.5B sizes",
                                       "qwen2.5-7b": "Qwen2.5-7B sizes"}[a.shape]
-    full_layers = raw["num_hidden_layers"]
+    full_layers = len(raw["layers"]) if other else raw["num_hidden_layers"]
     layers = full_layers if a.model else (a.layers or full_layers)
     f32 = a.dtype in ("f32", "fp32", "float32")
     elt = 4 if f32 else 2
@@ -884,7 +887,12 @@ def main() -> int:
     line = {}
     if "headline" in only:
         max_batch = max([a.batch, *points_b])
-        b = DecodeBench(a, raw, layers, a.dtype, max_batch, a.context + 4 * (a.steps + a.warmup) + max_batch + 64, load_dir=a.model)
+        b = DecodeBench(a, raw, layers, a.dtype, max_batch, a.context + 4 * (a.steps + a.warmup) + max_batch + 64, load_dir=a.model,
+                        vocab=raw.get("vocab") if other else None)
+        if other:  # what a decode step has to read: every weight once, and per live request what each cache group keeps
+            held = a.context + a.warmup + a.steps * 3 // 2
+            per_request = sum(len(g.runs) * g.need.elements_per_token() * min(held, g.need.window or held) for g in b.runner.cache.groups)
+            other_bytes = b.runner.memory_plan()["weights_bytes"] + elt * per_request * a.batch
         clocks = ClockSampler()
         clocks.start()
         times, launches = b.time_decode(a.batch, a.context, a.steps, a.warmup, profile=a.profile == "decode")
@@ -901,14 +909,18 @@ def main() -> int:
         if not a.no_points:
             pms = b.time_prefill(a.prefill, a.warmup, profile=a.profile == "prefill")
             prefill = {"value": round(a.prefill * 1000.0 / pms, 1), "tokens": a.prefill, "ms": round(pms, 3),
-                       "frac": round(prefill_flops(raw, layers, a.prefill) / (pms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}
+                       "frac": None if other else round(prefill_flops(raw, layers, a.prefill) / (pms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}
         b.runner.check_device_status()  # raises if a tensor-core kernel gave up one of its bounded waits
         b.release_all()
         del b
         free_device_memory()
 
         # the median block ran at contexts of about context + warmup + 1.5 * steps tokens
-        nbytes = decode_bytes(raw, layers, a.batch, a.context + a.warmup + a.steps * 3 // 2, elt)
+        if other:
+            describe = lambda **kw: {"architecture": raw.get("architecture"), "layers": layers, "page_size": PAGE, **kw}
+        else:
+            describe = lambda **kw: config_block(raw, layers, **kw)
+        nbytes = other_bytes if other else decode_bytes(raw, layers, a.batch, a.context + a.warmup + a.steps * 3 // 2, elt)
         achieved = nbytes / (ms_step * 1e-3) / 1e9
         line = {
             "metric": f"decode tokens/s ({name}, batch {a.batch}, {a.context}-token contexts)",
@@ -917,8 +929,8 @@ def main() -> int:
             "vs_baseline": round(value / PUBLISHED_DECODE_B8, 2) if a.shape == "qwen2.5-0.5b" and not a.model else None,
             "dtype": "fp32" if f32 else "bf16",
             "data": "synthetic: seeded uniform random token ids, random-init weights N(0, 0.02) drawn on the device",
-            "config": config_block(
-                raw, layers, model=name, global_batch=a.batch, seq_len=a.context, parallelism="single GPU",
+            "config": describe(
+                model=name, global_batch=a.batch, seq_len=a.context, parallelism="single GPU",
                 l2="inputs larger than L2 (weights read every step)",
                 timed="model + sampler + token copy to host, CUDA events, median of 3 blocks of K steps",
                 baseline="reference decode batch 8 on RX 7900 XTX, f32: 626 tok/s", peaks=pk["source"]),
