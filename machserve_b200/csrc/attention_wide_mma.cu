@@ -5,8 +5,8 @@
 // portion; MT = 4, 2 or 1 as the value columns leave registers, so that a tile of keys is staged once for up to 64 rows),
 // or, HEADS, up to 16 query heads of one token that share a key head (a decoding row: the heads of a group, or all heads
 // over a latent cache, fill the tensor core's 16 rows).  Wide values do not fit one warp's registers, so the
-// warps divide the work of a tile of 64 keys twice: for S = Q K^T each warp takes 16 of the keys (over all dk), for
-// O += P V each warp takes a quarter of the value columns (over all 64 keys); the probabilities cross between the two
+// warps divide the work of a tile of 64 keys twice: for S = Q K^T each warp takes its 16 or 8 of the keys (over all dk),
+// for O += P V each warp takes its share of the value columns (over all 64 keys); the probabilities cross between the two
 // through shared memory, and the row maxima through a small array.  Keys come in by 16-byte asynchronous copies through
 // the block table; with a latent cache the value tile IS the key tile.  Scores, maxima, sums and O are float32; Q, K,
 // V and P enter the tensor core as bfloat16.  Exponentials are 2^x with the scale folded in.
@@ -18,19 +18,26 @@
 
 #define AWM_KT 64
 #define AWM_ROWS 16
-#define AWM_WARPS 4
 
-// DVW: value columns a warp owns (the block covers 4 * DVW >= dv).  MT: tiles of 16 query rows a block attends.
-template <int DVW, int MT, bool SEPARATE_V, bool HEADS>
-__global__ void __launch_bounds__(AWM_WARPS * 32)
+// NW: warps of a block, 4, or 8 for decoding rows where the values are 256 or more columns wide (half the accumulators
+// a warp, twice the warps an SM).  DVW: value columns a warp owns (the block covers NW * DVW >= dv).
+// MT: tiles of 16 query rows a block attends.  A warp takes 64 / NW keys of a tile in the score phase.
+__device__ __forceinline__ void awm_ldmatrix_x2(unsigned& r0, unsigned& r1, const void* p) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2];\n" : "=r"(r0), "=r"(r1) : "r"(ms_smem_addr(p)));
+}
+
+template <int DVW, int MT, int NW, bool SEPARATE_V, bool HEADS>
+__global__ void __launch_bounds__(NW * 32)
 attention_wide_mma_kernel(const float* __restrict__ q, const __nv_bfloat16* __restrict__ k_pages,
                           const __nv_bfloat16* __restrict__ v_pages, __nv_bfloat16* __restrict__ out,
                           const float* __restrict__ sinks, const int* __restrict__ positions, const int* __restrict__ slots,
                           const int* __restrict__ block_table, int max_pages, int num_pages, const int* __restrict__ unit_row0,
                           const int* __restrict__ unit_rows, int hq, int hkv, int dk, int dv, int vw, int page_size, int window,
                           float scale_log2, int splits, float* __restrict__ scratch, int stages) {
-  constexpr int DVP = 4 * DVW;
+  constexpr int DVP = NW * DVW;
   constexpr int ROWS = AWM_ROWS * MT;
+  constexpr int KW = AWM_KT / NW;  // keys of a tile a warp scores: 16 or 8
+  constexpr int NS = KW / 8;       // tiles of 8 keys among them
   extern __shared__ __align__(16) unsigned char awm_smem[];
   const int ks_stride = dk + 8;          // elements of a row of the Q and K tiles
   constexpr int VS = DVP + 8;            // elements of a row of a separate V tile
@@ -40,7 +47,7 @@ attention_wide_mma_kernel(const float* __restrict__ q, const __nv_bfloat16* __re
   __nv_bfloat16* k_ring = q_s + ROWS * ks_stride;                                   // [stages][64][dk + 8] (+ slack: V columns past dk)
   __nv_bfloat16* v_ring = SEPARATE_V ? k_ring + stages * k_elems + DVP : k_ring;    // [stages][64][DVP + 8], or the key tiles
   __nv_bfloat16* p_s = (SEPARATE_V ? v_ring + stages * v_elems : k_ring + stages * k_elems + DVP);  // [ROWS][64 + 8]
-  float* red = reinterpret_cast<float*>(p_s + ROWS * PS);                           // [4][ROWS]
+  float* red = reinterpret_cast<float*>(p_s + ROWS * PS);                           // [NW][ROWS]
   const int v_stride = SEPARATE_V ? VS : ks_stride;
 
   ms_pdl_trigger();
@@ -102,9 +109,10 @@ attention_wide_mma_kernel(const float* __restrict__ q, const __nv_bfloat16* __re
   const int k_chunks = dk / 8, v_chunks = (dv + 7) / 8;  // 16-byte pieces of a key row, of a value row
   const int first_tile = lo_key / AWM_KT, last_tile = last_pos / AWM_KT;
 
-  // A tile's copy: two threads a key row, each its half of the row's 16-byte pieces; one page look-up a thread and tile.
+  // A tile's copy: two (or four) threads a key row, each its share of the row's 16-byte pieces; one page look-up a thread and tile.
+  constexpr int TPR = NW / 2;  // threads a row
   auto request = [&](int tile, int buf) {
-    const int j = threadIdx.x >> 1, key = tile * AWM_KT + j;
+    const int j = threadIdx.x / TPR, key = tile * AWM_KT + j;
     bool ok = key >= lo_key && key <= last_pos;
     size_t at = 0;
     if (ok) {
@@ -114,11 +122,11 @@ attention_wide_mma_kernel(const float* __restrict__ q, const __nv_bfloat16* __re
     }
     __nv_bfloat16* kd = k_ring + buf * k_elems + j * ks_stride;
     const __nv_bfloat16* ksrc = k_pages + at * dk;
-    for (int piece = threadIdx.x & 1; piece < k_chunks; piece += 2) ms_cp_async16(kd + piece * 8, ksrc + piece * 8, ok);
+    for (int piece = threadIdx.x % TPR; piece < k_chunks; piece += TPR) ms_cp_async16(kd + piece * 8, ksrc + piece * 8, ok);
     if (SEPARATE_V) {
       __nv_bfloat16* vd = v_ring + buf * v_elems + j * VS;
       const __nv_bfloat16* vsrc = v_pages + at * vw;
-      for (int piece = threadIdx.x & 1; piece < DVP / 8; piece += 2) ms_cp_async16(vd + piece * 8, vsrc + piece * 8, ok && piece < v_chunks);
+      for (int piece = threadIdx.x % TPR; piece < DVP / 8; piece += TPR) ms_cp_async16(vd + piece * 8, vsrc + piece * 8, ok && piece < v_chunks);
     }
     ms_cp_async_commit();
   };
@@ -148,33 +156,36 @@ attention_wide_mma_kernel(const float* __restrict__ q, const __nv_bfloat16* __re
     const __nv_bfloat16* k_s = k_ring + buf * k_elems;
     const __nv_bfloat16* v_s = SEPARATE_V ? v_ring + buf * v_elems : k_s;
 
-    // S for this warp's 16 keys (rows [16 * warp, 16 * warp + 16) of the tile), over all dk, for every tile of rows
-    float s[MT][2][4];
+    // S for this warp's KW keys (rows [KW * warp, KW * warp + KW) of the tile), over all dk, for every tile of rows
+    float s[MT][NS][4];
 #pragma unroll
     for (int t = 0; t < MT; ++t)
 #pragma unroll
-      for (int n = 0; n < 2; ++n)
+      for (int n = 0; n < NS; ++n)
 #pragma unroll
         for (int i = 0; i < 4; ++i) s[t][n][i] = 0.f;
-    const int krow0 = 16 * warp;
+    const int krow0 = KW * warp;
 #pragma unroll 2
     for (int ks = 0; ks < dk / 16; ++ks) {
       unsigned b[4];
-      ms_ldmatrix_x4(b[0], b[1], b[2], b[3], k_s + (krow0 + within + 8 * (mat >> 1)) * ks_stride + ks * 16 + 8 * (mat & 1));
+      if (NS == 2)
+        ms_ldmatrix_x4(b[0], b[1], b[2], b[3], k_s + (krow0 + within + 8 * (mat >> 1)) * ks_stride + ks * 16 + 8 * (mat & 1));
+      else
+        awm_ldmatrix_x2(b[0], b[1], k_s + (krow0 + within) * ks_stride + ks * 16 + 8 * (mat & 1));
 #pragma unroll
       for (int t = 0; t < MT; ++t) {
         if (t >= live_tiles) continue;
         unsigned a[4];
         ms_ldmatrix_x4(a[0], a[1], a[2], a[3], q_s + (t * AWM_ROWS + within + 8 * (mat & 1)) * ks_stride + ks * 16 + 8 * (mat >> 1));
         ms_mma_bf16(s[t][0], a, b[0], b[1]);
-        ms_mma_bf16(s[t][1], a, b[2], b[3]);
+        if (NS == 2) ms_mma_bf16(s[t][NS - 1], a, b[2], b[3]);
       }
     }
 #pragma unroll
     for (int t = 0; t < MT; ++t) {
       float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
-      for (int n = 0; n < 2; ++n)
+      for (int n = 0; n < NS; ++n)
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
           const int r = i >> 1;
@@ -201,23 +212,25 @@ attention_wide_mma_kernel(const float* __restrict__ q, const __nv_bfloat16* __re
 #pragma unroll
       for (int r = 0; r < 2; ++r) {
         const int row = t * AWM_ROWS + (lane >> 2) + 8 * r;
-        const float top = fmaxf(fmaxf(red[row], red[ROWS + row]), fmaxf(red[2 * ROWS + row], red[3 * ROWS + row]));
+        float top = red[row];
+#pragma unroll
+        for (int w = 1; w < NW; ++w) top = fmaxf(top, red[w * ROWS + row]);
         const float m_new = fmaxf(m[t][r], top);
         mu[r] = m_new == -INFINITY ? 0.f : m_new;  // nothing visible yet: any finite reference works
         corr[t][r] = ms_exp2(m[t][r] - mu[r]);      // 0 when the old maximum was -inf
         m[t][r] = m_new;
         l[t][r] *= corr[t][r];
       }
-      float p[2][4];
+      float p[NS][4];
 #pragma unroll
-      for (int n = 0; n < 2; ++n)
+      for (int n = 0; n < NS; ++n)
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
           p[n][i] = ms_exp2(s[t][n][i] - mu[i >> 1]);
           l[t][i >> 1] += p[n][i];  // (this warp's keys only: the warps' sums meet at the end)
         }
 #pragma unroll
-      for (int n = 0; n < 2; ++n) {
+      for (int n = 0; n < NS; ++n) {
         const int c = krow0 + n * 8 + col;
         *reinterpret_cast<unsigned*>(p_s + (t * AWM_ROWS + (lane >> 2)) * PS + c) = ms_pack_bf16(p[n][0], p[n][1]);
         *reinterpret_cast<unsigned*>(p_s + (t * AWM_ROWS + (lane >> 2) + 8) * PS + c) = ms_pack_bf16(p[n][2], p[n][3]);
@@ -278,7 +291,10 @@ attention_wide_mma_kernel(const float* __restrict__ q, const __nv_bfloat16* __re
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
       const int row = t * AWM_ROWS + (lane >> 2) + 8 * r;
-      l[t][r] = (red[row] + red[ROWS + row]) + (red[2 * ROWS + row] + red[3 * ROWS + row]);
+      float sum = red[row];
+#pragma unroll
+      for (int w = 1; w < NW; ++w) sum += red[w * ROWS + row];  // in warp order
+      l[t][r] = sum;
     }
 
   if (splits > 1) {  // (O, m, l) of this split: [item][split][16][DVP + 2]  (decoding rows: one tile of 16 rows)
@@ -375,13 +391,16 @@ attention_wide_mma_merge_kernel(const float* __restrict__ scratch, __nv_bfloat16
 }
 
 static int awm_dvp(int dv) { return dv <= 64 ? 64 : dv <= 128 ? 128 : dv <= 256 ? 256 : 512; }
-// tiles of 16 rows a block attends when the rows are a portion's: as many as leave the value columns their registers
+// tiles of 16 rows a block of four warps attends when the rows are a portion's: as many as leave the value columns their
+// registers.  (Decoding rows at 256 or more value columns take blocks of eight warps: measured at latents of 256 and 512,
+// 64 rows under a window of 1,024 went from 55, 121 and 158 us to 45, 86 and 114; portions with eight warps and twice the
+// rows a block were slower, 795 against 570 us at the smallest: one block of 180 registers a thread per SM.)
 static int awm_row_tiles(int dvp) { return dvp <= 128 ? 4 : dvp == 256 ? 2 : 1; }
 
 static size_t awm_smem_bytes(int dk, int dvp, bool separate_v, int rows, int stages = 1) {
   size_t elems = (size_t)rows * (dk + 8) + (size_t)stages * AWM_KT * (dk + 8) + dvp + (size_t)rows * (AWM_KT + 8);
   if (separate_v) elems += (size_t)stages * AWM_KT * (dvp + 8);
-  return elems * 2 + 4 * rows * sizeof(float) + 16;
+  return elems * 2 + 8 * rows * sizeof(float) + 16;
 }
 
 MS_API int ms_attention_wide_mma_supports(int dk, int dv, int vw, int separate_v) {
@@ -398,15 +417,15 @@ MS_API long long ms_attention_wide_mma_scratch_words(int items, int dv, int spli
   return splits > 1 ? (long long)items * splits * AWM_ROWS * (awm_dvp(dv) + 2) : 0;
 }
 
-template <int DVW, int MT>
+template <int DVW, int MT, int DVW_H, int NW_H>
 static int awm_launch(bool separate_v, bool heads, unsigned blocks, size_t smem, cudaStream_t stream, const float* q,
                       const __nv_bfloat16* k_pages, const __nv_bfloat16* v_pages, __nv_bfloat16* out, const float* sinks,
                       const int* positions, const int* slots, const int* block_table, int max_pages, int num_pages,
                       const int* unit_row0, const int* unit_rows, int hq, int hkv, int dk, int dv, int vw, int page_size, int window,
                       float scale_log2, int splits, float* scratch, int stages) {
-#define MS_AWM_GO(M, SV, H)                                                                                                \
+#define MS_AWM_GO(W, M, N, SV, H)                                                                                              \
   do {                                                                                                                     \
-    auto kern = attention_wide_mma_kernel<DVW, M, SV, H>;                                                                  \
+    auto kern = attention_wide_mma_kernel<W, M, N, SV, H>;                                                                  \
     static size_t configured = 0;                                                                                          \
     if (smem > configured) {                                                                                               \
       cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);                  \
@@ -414,14 +433,14 @@ static int awm_launch(bool separate_v, bool heads, unsigned blocks, size_t smem,
       configured = smem;                                                                                                   \
     }                                                                                                                      \
     MS_LAUNCH_RESULT("attention_wide_mma",                                                                                 \
-                     ms_launch(kern, dim3(blocks), dim3(AWM_WARPS * 32), smem, stream, 1, true, q, k_pages, v_pages, out, sinks, \
+                     ms_launch(kern, dim3(blocks), dim3(N * 32), smem, stream, 1, true, q, k_pages, v_pages, out, sinks, \
                                positions, slots, block_table, max_pages, num_pages, unit_row0, unit_rows, hq, hkv, dk, dv, vw,    \
                                page_size, window, scale_log2, splits, scratch, stages));                                   \
   } while (0)
-  if (separate_v && heads) MS_AWM_GO(1, true, true);
-  else if (separate_v) MS_AWM_GO(MT, true, false);
-  else if (heads) MS_AWM_GO(1, false, true);
-  else MS_AWM_GO(MT, false, false);
+  if (separate_v && heads) MS_AWM_GO(DVW_H, 1, NW_H, true, true);
+  else if (separate_v) MS_AWM_GO(DVW, MT, 4, true, false);
+  else if (heads) MS_AWM_GO(DVW_H, 1, NW_H, false, true);
+  else MS_AWM_GO(DVW, MT, 4, false, false);
 #undef MS_AWM_GO
   return 0;
 }
@@ -458,10 +477,10 @@ MS_API int ms_attention_wide_mma(const float* q, const void* k_pages, const void
                     (const __nv_bfloat16*)v_pages, (__nv_bfloat16*)out, sinks, positions, slots, block_table, max_pages, num_pages, \
                     unit_row0, unit_rows, hq, hkv, dk, dv, vw, page_size, window, scale_log2, splits, scratch, stages
   int rc;
-  if (dvp == 64) rc = awm_launch<16, 4>(MS_AWM_ARGS);
-  else if (dvp == 128) rc = awm_launch<32, 4>(MS_AWM_ARGS);
-  else if (dvp == 256) rc = awm_launch<64, 2>(MS_AWM_ARGS);
-  else rc = awm_launch<128, 1>(MS_AWM_ARGS);
+  if (dvp == 64) rc = awm_launch<16, 4, 16, 4>(MS_AWM_ARGS);
+  else if (dvp == 128) rc = awm_launch<32, 4, 32, 4>(MS_AWM_ARGS);
+  else if (dvp == 256) rc = awm_launch<64, 2, 32, 8>(MS_AWM_ARGS);
+  else rc = awm_launch<128, 1, 64, 8>(MS_AWM_ARGS);
 #undef MS_AWM_ARGS
   if (rc) return rc;
   if (splits > 1)
