@@ -512,6 +512,36 @@ def test_unequal_requests_side_by_side_on_reused_pages(model_root, name, dtype):
             assert np.array_equal(got[rid], alone[rid]), f"float32 logits of {rid} must not depend on the batch or the pages"
 
 
+@pytest.mark.parametrize("name,dtype", [("T", "bfloat16"), ("U", "bfloat16"), ("P", "float32")])
+def test_many_rows_decode_together(model_root, name, dtype):
+    """24 requests of unequal lengths decode side by side for several steps (more rows than the few-row products take,
+    so the products go to the library), then half of them end and others go on: each against itself alone."""
+    from machserve_b200.engine.replay import make_replay_runner, replay
+
+    d = make_model_dir(model_root, name)
+    vocab = CASES[name]["config"]["vocab"]
+    lens = [5 + 3 * i for i in range(24)]
+    reqs = {f"r{i}": random_tokens(vocab, n + 6, 500 + i) for i, n in enumerate(lens)}
+    steps, st = [], 0
+    for rid, toks in reqs.items():  # the prompts, one request a step
+        steps.append({"step": st, "entries": [{"id": rid, "tokens": toks[:-6], "want": [len(toks) - 7]}], "end": []})
+        st += 1
+    for k in range(6):  # six decoding steps; after the third, the even requests are left out (they end early)
+        live = [rid for i, rid in enumerate(reqs) if k < 3 or i % 2]
+        ended = [rid for i, rid in enumerate(reqs) if (k == 2 and i % 2 == 0) or (k == 5 and i % 2)]
+        steps.append({"step": st, "entries": [{"id": rid, "tokens": [reqs[rid][len(reqs[rid]) - 6 + k]], "want": [0]} for rid in live],
+                      "end": ended})
+        st += 1
+    runner = make_replay_runner(d, dtype, 24 * 128, CASES[name]["page"], 24)
+    got = collect_rows(steps, replay(runner, steps))
+    runner.cache.check()
+    assert not runner.cache.requests
+    for i, (rid, toks) in enumerate(reqs.items()):
+        n = len(toks) if i % 2 else len(toks) - 3
+        want = _want(d, dtype, toks[:n])[len(toks) - 7 : n]
+        assert_close(got[rid], want, _tol(dtype), f"{name} {dtype} {rid} among 24")
+
+
 @pytest.mark.parametrize("name", ["P", "Q"])
 def test_long_decoding(model_root, name):
     """Token by token from the first token on, far past every window and over many pages."""
