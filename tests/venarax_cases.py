@@ -108,6 +108,18 @@ CASES = {
         },
         seed=16, page=16,
     ),
+    # odd sizes everywhere: a width, feed-forward, vocabulary and head sizes that no vector access and no tensor-core tile fits
+    "V": dict(
+        config={
+            "architecture": "Venarax", "vocab": 131, "width": 50, "norm": {"eps": 1e-6},
+            "layers": [
+                {**_latent(3, 7, 6, 9, 10, 0.3, 777.0, 6, 13), "mlp": _mlp(37, 1.7)},
+                {**_attention(5, 1, 5, 3, 0.4, 0.9, 7), "mlp": _mlp(41, 1.7)},
+            ],
+            "loop": {"start": 1, "stop": 2, "times": 2},
+        },
+        seed=17, page=8,
+    ),
 }
 
 
