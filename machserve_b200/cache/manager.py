@@ -97,9 +97,12 @@ class CacheManager:
 
     def _first_needed_page(self, group: CacheGroup, query_pos: int) -> int:
         """The first logical page a query at `query_pos` (and every later one) can still read."""
-        if group.need.window is None:
-            return 0
-        return max(0, query_pos - group.need.window + 1) // self.page_size
+        first = 0
+        if group.need.window is not None:
+            first = max(0, query_pos - group.need.window + 1)
+        if getattr(group.need, "chunk", None):  # a query reads its own chunk only, and so does every later one
+            first = max(first, query_pos // group.need.chunk * group.need.chunk)
+        return first // self.page_size
 
     def pages_missing(self, req: Hashable, new_len: int) -> List[int]:
         """Per group, how many pages `reserve(req, new_len)` would take."""
@@ -153,7 +156,7 @@ class CacheManager:
             raise ValueError(f"request {req!r}: commit of {new_len} tokens, only {rc.reserved} are reserved")
         rc.num_tokens = max(rc.num_tokens, new_len)
         for g, table in zip(self.groups, rc.tables):
-            if g.need.window is None:
+            if g.need.window is None and not getattr(g.need, "chunk", None):
                 continue
             keep_from = self._first_needed_page(g, rc.num_tokens)
             for i in range(min(keep_from, len(table))):

@@ -11,3 +11,4 @@ from .base import (  # noqa: F401
 from .spec import LayerSpec, ModelSpec, PartSpec, RunSpec, part  # noqa: F401
 from .qwen2 import Qwen2Config  # noqa: F401
 from .venarax import VenaraxConfig  # noqa: F401
+from .fozutar import FozutarConfig  # noqa: F401

@@ -153,4 +153,15 @@ def load_config(model_dir) -> ModelConfig:
         raise ConfigError(f"{path}: not valid JSON ({e})") from None
     if not isinstance(raw, dict):
         raise ConfigError(f"{path}: the top level must be an object")
-    return config_from_json(raw)
+    config = config_from_json(raw)
+    # a design may leave sizes to the shapes of its tensors: such a configuration asks for them here
+    if getattr(config, "needs_tensor_shapes", None) is not None and config.needs_tensor_shapes():
+        from ..weights.safetensors_io import open_model_files
+
+        entries, files = open_model_files(model_dir)
+        try:
+            config = config.with_tensor_shapes({name: tuple(e.shape) for name, e in entries.items()})
+        finally:
+            for f in files:
+                f.close()
+    return config

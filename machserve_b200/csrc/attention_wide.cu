@@ -25,7 +25,7 @@ __global__ void __launch_bounds__(W * 32)
 attention_wide_kernel(const float* __restrict__ q, const TC* __restrict__ k_pages, const TC* __restrict__ v_pages,
                       TC* __restrict__ out, const float* __restrict__ sinks, const int* __restrict__ positions,
                       const int* __restrict__ slots, const int* __restrict__ block_table, int max_pages, int num_pages,
-                      int tokens, int hq, int hkv, int dk, int dv, int vw, int page_size, int window, float scale) {
+                      int tokens, int hq, int hkv, int dk, int dv, int vw, int page_size, int window, float scale, MsScoreExtras ex) {
   extern __shared__ __align__(16) float aw_smem[];
   float* q_s = aw_smem;                                  // [R][dk]
   float* k_all = q_s + (size_t)R * dk;                   // [W][32][AW_KC + 1]
@@ -54,6 +54,7 @@ attention_wide_kernel(const float* __restrict__ q, const TC* __restrict__ k_page
     seq[r] = r < live_rows ? slots[tok0 + r * tok_step] : -1;
     pos[r] = seq[r] >= 0 ? positions[tok0 + r * tok_step] : -1;
     first[r] = (window > 0 && pos[r] - window + 1 > 0) ? pos[r] - window + 1 : 0;
+    if (ex.chunk > 0 && pos[r] >= 0) first[r] = max(first[r], pos[r] / ex.chunk * ex.chunk);
   }
   for (int e = threadIdx.x; e < R * dk; e += blockDim.x) {
     const int r = e / dk, d = e - r * dk;
@@ -151,7 +152,12 @@ attention_wide_kernel(const float* __restrict__ q, const TC* __restrict__ k_page
         pr[r] = 0.f;
         if (!((run >> r) & 1u) || tile * 32 > pos[r]) continue;  // (the same for the whole warp)
         const bool valid = base >= 0 && key >= first[r] && key <= pos[r];
-        const float sc = valid ? dot[r] * scale : -INFINITY;
+        float sc = -INFINITY;
+        if (valid) {
+          sc = dot[r] * scale;
+          if (ex.softcap > 0.f) sc = ex.softcap * tanhf(sc / ex.softcap);
+          if (ex.dist_bias) sc += ex.dist_bias[(size_t)(head0 + r * head_step) * ex.dist_len + min(pos[r] - key, ex.dist_len - 1)];
+        }
         const float tile_max = ms_warp_max(sc);
         const float m_new = fmaxf(m[r], tile_max);
         pr[r] = (valid && m_new > -INFINITY) ? expf(sc - m_new) : 0.f;
@@ -232,7 +238,7 @@ template <typename TC, int W, int NACC, int R, bool HEADS>
 static int launch_attention_wide_form(const float* q, const void* k_pages, const void* v_pages, void* out, const float* sinks,
                                       const int* positions, const int* slots, const int* block_table, int max_pages, int num_pages,
                                       int tokens, int hq, int hkv, int dk, int dv, int vw, int page_size, int window, float scale,
-                                      cudaStream_t stream) {
+                                      MsScoreExtras ex, cudaStream_t stream) {
   const int groups = hq / hkv;
   const size_t smem = ((size_t)R * dk + (size_t)W * 32 * (AW_KC + 1) + (size_t)W * R * (dv + 2)) * sizeof(float);
   MS_REQUIRE(smem <= 200 * 1024, "attention_wide: keys of %d coordinates need %zu bytes of shared memory", dk, smem);
@@ -246,7 +252,7 @@ static int launch_attention_wide_form(const float* q, const void* k_pages, const
     configured = smem;
   }
   kern<<<blocks, W * 32, smem, stream>>>(q, (const TC*)k_pages, (const TC*)v_pages, (TC*)out, sinks, positions, slots, block_table,
-                                         max_pages, num_pages, tokens, hq, hkv, dk, dv, vw, page_size, window, scale);
+                                         max_pages, num_pages, tokens, hq, hkv, dk, dv, vw, page_size, window, scale, ex);
   MS_LAUNCH_CHECK("attention_wide");
   return 0;
 }
@@ -258,9 +264,9 @@ template <typename TC, int W, int NACC, int R>
 static int launch_attention_wide(const float* q, const void* k_pages, const void* v_pages, void* out, const float* sinks,
                                  const int* positions, const int* slots, const int* block_table, int max_pages, int num_pages,
                                  int tokens, int hq, int hkv, int dk, int dv, int vw, int page_size, int window, float scale,
-                                 bool heads, cudaStream_t stream) {
+                                 MsScoreExtras ex, bool heads, cudaStream_t stream) {
 #define MS_AW_ARGS q, k_pages, v_pages, out, sinks, positions, slots, block_table, max_pages, num_pages, tokens, hq, hkv, dk, dv, vw, \
-                   page_size, window, scale, stream
+                   page_size, window, scale, ex, stream
   if (!heads) return launch_attention_wide_form<TC, W, NACC, R, false>(MS_AW_ARGS);
   const int groups = hq / hkv;
   int sms = 148;
@@ -282,11 +288,12 @@ static int launch_attention_wide(const float* q, const void* k_pages, const void
 // q [tokens, hq*dk] float32; out [tokens, hq*dv] in the cache's type.  window <= 0: every earlier key is visible.
 // share_rows: the step has rows that follow one another in a sequence, and R consecutive rows share a block; else the
 // query heads of a token that share a key head do.  sinks: float32 [hq] or null.
-MS_API int ms_attention_wide(const float* q, const void* k_pages, const void* v_pages, void* out, int cache_dtype,
-                             const float* sinks, const int* positions, const int* slots, const int* block_table, int max_pages,
-                             int num_pages, int tokens, int hq, int hkv, int dk, int dv, int vw, int page_size, int window,
-                             float scale, int share_rows, cudaStream_t stream) {
+static int attention_wide_entry(const float* q, const void* k_pages, const void* v_pages, void* out, int cache_dtype,
+                                const float* sinks, const int* positions, const int* slots, const int* block_table, int max_pages,
+                                int num_pages, int tokens, int hq, int hkv, int dk, int dv, int vw, int page_size, int window,
+                                float scale, MsScoreExtras ex, int share_rows, cudaStream_t stream) {
   if (tokens == 0) return 0;
+  MS_REQUIRE(ex.dist_bias == nullptr || ex.dist_len > 0, "attention_wide: a distance bias without entries");
   MS_REQUIRE(tokens > 0 && hq > 0 && hkv > 0 && hq % hkv == 0, "attention_wide: bad head counts hq=%d hkv=%d", hq, hkv);
   MS_REQUIRE(dk > 0 && dv > 0 && dv <= 512 && vw >= dv, "attention_wide: widths dk=%d dv=%d (of %d) are not covered", dk, dv, vw);
   MS_REQUIRE(page_size > 0 && max_pages > 0 && num_pages > 0, "attention_wide: bad cache sizes");
@@ -295,15 +302,15 @@ MS_API int ms_attention_wide(const float* q, const void* k_pages, const void* v_
   do {                                                                                                                  \
     if (dv <= 64)                                                                                                       \
       return launch_attention_wide<TC, 8, 2, 8>(q, k_pages, v_pages, out, sinks, positions, slots, block_table, max_pages, num_pages, \
-                                                tokens, hq, hkv, dk, dv, vw, page_size, window, scale, heads, stream);          \
+                                                tokens, hq, hkv, dk, dv, vw, page_size, window, scale, ex, heads, stream);          \
     if (dv <= 128)                                                                                                      \
       return launch_attention_wide<TC, 4, 4, 8>(q, k_pages, v_pages, out, sinks, positions, slots, block_table, max_pages, num_pages, \
-                                                tokens, hq, hkv, dk, dv, vw, page_size, window, scale, heads, stream);          \
+                                                tokens, hq, hkv, dk, dv, vw, page_size, window, scale, ex, heads, stream);          \
     if (dv <= 256)                                                                                                      \
       return launch_attention_wide<TC, 4, 8, 4>(q, k_pages, v_pages, out, sinks, positions, slots, block_table, max_pages, num_pages, \
-                                                tokens, hq, hkv, dk, dv, vw, page_size, window, scale, heads, stream);          \
+                                                tokens, hq, hkv, dk, dv, vw, page_size, window, scale, ex, heads, stream);          \
     return launch_attention_wide<TC, 4, 16, 2>(q, k_pages, v_pages, out, sinks, positions, slots, block_table, max_pages, num_pages, \
-                                               tokens, hq, hkv, dk, dv, vw, page_size, window, scale, heads, stream);           \
+                                               tokens, hq, hkv, dk, dv, vw, page_size, window, scale, ex, heads, stream);           \
   } while (0)
   if (cache_dtype == MS_F32)
     MS_AW_CASE(float);
@@ -312,4 +319,25 @@ MS_API int ms_attention_wide(const float* q, const void* k_pages, const void* v_
 #undef MS_AW_CASE
   MS_REQUIRE(false, "attention_wide: unknown cache dtype %d", cache_dtype);
   return 0;
+}
+
+MS_API int ms_attention_wide(const float* q, const void* k_pages, const void* v_pages, void* out, int cache_dtype,
+                             const float* sinks, const int* positions, const int* slots, const int* block_table, int max_pages,
+                             int num_pages, int tokens, int hq, int hkv, int dk, int dv, int vw, int page_size, int window,
+                             float scale, int share_rows, cudaStream_t stream) {
+  return attention_wide_entry(q, k_pages, v_pages, out, cache_dtype, sinks, positions, slots, block_table, max_pages, num_pages, tokens,
+                              hq, hkv, dk, dv, vw, page_size, window, scale, MsScoreExtras{0.f, nullptr, 0, 0}, share_rows, stream);
+}
+
+// The same with what may come between the scaled score and the softmax (common.cuh, MsScoreExtras): a soft cap
+// softcap * tanh(score / softcap), a learned bias by head and distance dist_bias[h][min(i - j, dist_len - 1)] (float32
+// [hq, dist_len], not scaled), and a mask by chunks: position i sees the keys j <= i of its own chunk floor(i / chunk) only.
+MS_API int ms_attention_wide_scored(const float* q, const void* k_pages, const void* v_pages, void* out, int cache_dtype,
+                                    const float* sinks, const int* positions, const int* slots, const int* block_table, int max_pages,
+                                    int num_pages, int tokens, int hq, int hkv, int dk, int dv, int vw, int page_size, int window,
+                                    float scale, float softcap, const float* dist_bias, int dist_len, int chunk, int share_rows,
+                                    cudaStream_t stream) {
+  return attention_wide_entry(q, k_pages, v_pages, out, cache_dtype, sinks, positions, slots, block_table, max_pages, num_pages, tokens,
+                              hq, hkv, dk, dv, vw, page_size, window, scale, MsScoreExtras{softcap, dist_bias, dist_len, chunk}, share_rows,
+                              stream);
 }

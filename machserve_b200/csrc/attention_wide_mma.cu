@@ -33,7 +33,7 @@ attention_wide_mma_kernel(const float* __restrict__ q, const __nv_bfloat16* __re
                           const float* __restrict__ sinks, const int* __restrict__ positions, const int* __restrict__ slots,
                           const int* __restrict__ block_table, int max_pages, int num_pages, const int* __restrict__ unit_row0,
                           const int* __restrict__ unit_rows, int hq, int hkv, int dk, int dv, int vw, int page_size, int window,
-                          float scale_log2, int splits, float* __restrict__ scratch, int stages) {
+                          float scale_log2, int splits, float* __restrict__ scratch, int stages, MsScoreExtras ex) {
   constexpr int DVP = NW * DVW;
   constexpr int ROWS = AWM_ROWS * MT;
   constexpr int KW = AWM_KT / NW;  // keys of a tile a warp scores: 16 or 8
@@ -77,7 +77,8 @@ attention_wide_mma_kernel(const float* __restrict__ q, const __nv_bfloat16* __re
   if (seq < 0) return;
   pos0 = positions[row0];
   const int last_pos = HEADS ? pos0 : pos0 + live - 1;
-  const int lo_key = (window > 0 && pos0 - window + 1 > 0) ? pos0 - window + 1 : 0;
+  int lo_key = (window > 0 && pos0 - window + 1 > 0) ? pos0 - window + 1 : 0;
+  if (ex.chunk > 0) lo_key = max(lo_key, pos0 / ex.chunk * ex.chunk);  // (later rows of the tile begin there or later)
   // the two rows this thread holds in every accumulator of a tile of 16 rows: lane / 4 and lane / 4 + 8; their
   // ranges of visible keys
   int lo[MT][2], hi[MT][2];
@@ -89,6 +90,7 @@ attention_wide_mma_kernel(const float* __restrict__ q, const __nv_bfloat16* __re
       const int p = HEADS ? pos0 : pos0 + r;
       hi[t][i] = r < live ? p : -1;
       lo[t][i] = (window > 0 && p - window + 1 > 0) ? p - window + 1 : 0;
+      if (ex.chunk > 0) lo[t][i] = max(lo[t][i], p / ex.chunk * ex.chunk);
     }
 
   float o[MT][DVW / 8][4];
@@ -191,7 +193,20 @@ attention_wide_mma_kernel(const float* __restrict__ q, const __nv_bfloat16* __re
           const int r = i >> 1;
           const int key = key0 + krow0 + n * 8 + col + (i & 1);
           const bool ok = key >= lo[t][r] && key <= hi[t][r];
-          s[t][n][i] = ok ? s[t][n][i] * scale_log2 : -INFINITY;
+          float sc = -INFINITY;
+          if (ok) {
+            sc = s[t][n][i] * scale_log2;
+            if (ex.softcap > 0.f || ex.dist_bias) {  // back to natural units: the cap and the bias are not scaled
+              sc *= 0.6931471805599453f;
+              if (ex.softcap > 0.f) sc = ex.softcap * tanhf(sc / ex.softcap);
+              if (ex.dist_bias) {
+                const int head = HEADS ? head0 + t * AWM_ROWS + (lane >> 2) + 8 * r : head0;
+                sc += ex.dist_bias[(size_t)head * ex.dist_len + min(hi[t][r] - key, ex.dist_len - 1)];
+              }
+              sc *= MS_LOG2E;
+            }
+          }
+          s[t][n][i] = sc;
           mx[r] = fmaxf(mx[r], s[t][n][i]);
         }
 #pragma unroll
@@ -422,7 +437,7 @@ static int awm_launch(bool separate_v, bool heads, unsigned blocks, size_t smem,
                       const __nv_bfloat16* k_pages, const __nv_bfloat16* v_pages, __nv_bfloat16* out, const float* sinks,
                       const int* positions, const int* slots, const int* block_table, int max_pages, int num_pages,
                       const int* unit_row0, const int* unit_rows, int hq, int hkv, int dk, int dv, int vw, int page_size, int window,
-                      float scale_log2, int splits, float* scratch, int stages) {
+                      float scale_log2, int splits, float* scratch, int stages, MsScoreExtras ex) {
 #define MS_AWM_GO(W, M, N, SV, H)                                                                                              \
   do {                                                                                                                     \
     auto kern = attention_wide_mma_kernel<W, M, N, SV, H>;                                                                  \
@@ -435,7 +450,7 @@ static int awm_launch(bool separate_v, bool heads, unsigned blocks, size_t smem,
     MS_LAUNCH_RESULT("attention_wide_mma",                                                                                 \
                      ms_launch(kern, dim3(blocks), dim3(N * 32), smem, stream, 1, true, q, k_pages, v_pages, out, sinks, \
                                positions, slots, block_table, max_pages, num_pages, unit_row0, unit_rows, hq, hkv, dk, dv, vw,    \
-                               page_size, window, scale_log2, splits, scratch, stages));                                   \
+                               page_size, window, scale_log2, splits, scratch, stages, ex));                                \
   } while (0)
   if (separate_v && heads) MS_AWM_GO(DVW_H, 1, NW_H, true, true);
   else if (separate_v) MS_AWM_GO(DVW, MT, 4, true, false);
@@ -451,11 +466,12 @@ static int awm_launch(bool separate_v, bool heads, unsigned blocks, size_t smem,
 // ms_attention_wide_mma_tile_rows(dv) each (a tile of no rows does nothing).  heads != 0: `units` decoding rows, row
 // unit_row0[u] (or u, without a list; -1: none), each cut into `splits` runs of key tiles; scratch as
 // ms_attention_wide_mma_scratch_words says.
-MS_API int ms_attention_wide_mma(const float* q, const void* k_pages, const void* v_pages, void* out, const float* sinks,
-                                 const int* positions, const int* slots, const int* block_table, int max_pages, int num_pages,
-                                 const int* unit_row0, const int* unit_rows, int units, int heads, int hq, int hkv, int dk, int dv,
-                                 int vw, int page_size, int window, float scale, int splits, float* scratch, cudaStream_t stream) {
+static int awm_entry(const float* q, const void* k_pages, const void* v_pages, void* out, const float* sinks,
+                     const int* positions, const int* slots, const int* block_table, int max_pages, int num_pages,
+                     const int* unit_row0, const int* unit_rows, int units, int heads, int hq, int hkv, int dk, int dv,
+                     int vw, int page_size, int window, float scale, int splits, float* scratch, MsScoreExtras ex, cudaStream_t stream) {
   if (units == 0) return 0;
+  MS_REQUIRE(ex.dist_bias == nullptr || ex.dist_len > 0, "attention_wide_mma: a distance bias without entries");
   const bool separate_v = k_pages != v_pages;
   MS_REQUIRE(units > 0 && hq > 0 && hkv > 0 && hq % hkv == 0, "attention_wide_mma: bad sizes units=%d hq=%d hkv=%d", units, hq, hkv);
   MS_REQUIRE(ms_attention_wide_mma_supports(dk, dv, vw, separate_v), "attention_wide_mma: widths dk=%d dv=%d (rows of %d) are not covered",
@@ -475,7 +491,7 @@ MS_API int ms_attention_wide_mma(const float* q, const void* k_pages, const void
   const float scale_log2 = scale * MS_LOG2E;
 #define MS_AWM_ARGS separate_v, heads != 0, items * (unsigned)splits, smem, stream, q, (const __nv_bfloat16*)k_pages,         \
                     (const __nv_bfloat16*)v_pages, (__nv_bfloat16*)out, sinks, positions, slots, block_table, max_pages, num_pages, \
-                    unit_row0, unit_rows, hq, hkv, dk, dv, vw, page_size, window, scale_log2, splits, scratch, stages
+                    unit_row0, unit_rows, hq, hkv, dk, dv, vw, page_size, window, scale_log2, splits, scratch, stages, ex
   int rc;
   if (dvp == 64) rc = awm_launch<16, 4, 16, 4>(MS_AWM_ARGS);
   else if (dvp == 128) rc = awm_launch<32, 4, 32, 4>(MS_AWM_ARGS);
@@ -488,4 +504,23 @@ MS_API int ms_attention_wide_mma(const float* q, const void* k_pages, const void
                      ms_launch(attention_wide_mma_merge_kernel, dim3(items * AWM_ROWS), dim3(128), 0, stream, 1, true, (const float*)scratch,
                                (__nv_bfloat16*)out, sinks, slots, unit_row0, hq, hkv, dv, dvp, splits));
   return 0;
+}
+
+MS_API int ms_attention_wide_mma(const float* q, const void* k_pages, const void* v_pages, void* out, const float* sinks,
+                                 const int* positions, const int* slots, const int* block_table, int max_pages, int num_pages,
+                                 const int* unit_row0, const int* unit_rows, int units, int heads, int hq, int hkv, int dk, int dv,
+                                 int vw, int page_size, int window, float scale, int splits, float* scratch, cudaStream_t stream) {
+  return awm_entry(q, k_pages, v_pages, out, sinks, positions, slots, block_table, max_pages, num_pages, unit_row0, unit_rows, units,
+                   heads, hq, hkv, dk, dv, vw, page_size, window, scale, splits, scratch, MsScoreExtras{0.f, nullptr, 0, 0}, stream);
+}
+
+// The same with a soft cap, a bias by head and distance, and a mask by chunks (common.cuh, MsScoreExtras).
+MS_API int ms_attention_wide_mma_scored(const float* q, const void* k_pages, const void* v_pages, void* out, const float* sinks,
+                                        const int* positions, const int* slots, const int* block_table, int max_pages, int num_pages,
+                                        const int* unit_row0, const int* unit_rows, int units, int heads, int hq, int hkv, int dk,
+                                        int dv, int vw, int page_size, int window, float scale, int splits, float* scratch,
+                                        float softcap, const float* dist_bias, int dist_len, int chunk, cudaStream_t stream) {
+  return awm_entry(q, k_pages, v_pages, out, sinks, positions, slots, block_table, max_pages, num_pages, unit_row0, unit_rows, units,
+                   heads, hq, hkv, dk, dv, vw, page_size, window, scale, splits, scratch,
+                   MsScoreExtras{softcap, dist_bias, dist_len, chunk}, stream);
 }

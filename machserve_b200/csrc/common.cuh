@@ -18,6 +18,16 @@ enum MsDtype { MS_F32 = 0, MS_BF16 = 1 };
 
 void ms_set_error(const char* fmt, ...);
 
+// What an attention kernel may apply between the scaled score and the softmax, and a mask by chunks; all off when zero.
+//   score <- softcap * tanh(score / softcap); score += dist_bias[head * dist_len + min(i - j, dist_len - 1)];
+//   position i sees the keys j <= i with floor(j / chunk) == floor(i / chunk) only.
+struct MsScoreExtras {
+  float softcap;
+  const float* dist_bias;
+  int dist_len;
+  int chunk;
+};
+
 #define MS_REQUIRE(cond, ...)      \
   do {                             \
     if (!(cond)) {                 \

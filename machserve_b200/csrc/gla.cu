@@ -1,0 +1,198 @@
+// Gated linear attention: a recurrent mixer with a matrix state per head and a decay per key channel.
+//
+//   S_t = diag(a_t) S_(t-1) + k_t v_t^T        S: [dk, dv] per head, float32, one per request slot
+//   o_t = S_t^T (q_t * q_scale)
+//   a_t = sigmoid(z_t)^(1/tau),  z_t = W2 u_t + b2 (u_t the low-rank projection of the token), kept as its logarithm
+//         g_t = logsigmoid(z_t) / tau until the scan takes exp(g_t)
+//   y_t = o_t / rms(o_t) * w (per head, over dv, eps inside the root) * silu(gate_t)
+// Everything here is float32: the decays and their logarithms, the state, the sums, the norm and the gate.
+//
+// gla_decay:   g[t, n] = logsigmoid(sum_r W2[n, r] * u[t, r] + b2[n]) / tau; one thread an output.
+// gla_scan:    a block owns 32 value columns of one head of one sequence and goes through the sequence's rows of the step in
+//              order, from the state the step found to the state it leaves.  Thread (c, g) holds KPT consecutive key rows of
+//              column c in registers; q, k and exp(g) of TB tokens at a time are staged in shared memory; the partial
+//              outputs of the eight row groups are summed in group order.  The arithmetic of a token depends on the
+//              tokens before it alone, not on how the sequence was cut into steps or on what else is in the batch.
+// gla_output:  the norm over a head's dv outputs, its weight, and the gate; one warp a (token, head).
+#include "launch.cuh"
+
+#define GLA_COLS 32
+#define GLA_GROUPS 8
+#define GLA_TB 8
+
+template <typename TW>
+__global__ void gla_decay_kernel(const float* __restrict__ u, int ldu, const TW* __restrict__ w2, const float* __restrict__ b2, int rank,
+                                 float inv_tau, float* __restrict__ g, int n, size_t total) {
+  ms_pdl_trigger();
+  ms_pdl_wait();
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const size_t t = i / n;
+  const int c = (int)(i - t * n);
+  const float* ur = u + t * ldu;
+  const TW* wr = w2 + (size_t)c * rank;
+  float z = 0.f;
+  for (int r = 0; r < rank; ++r) z = fmaf(ms_to_float(wr[r]), ur[r], z);
+  z += b2 ? b2[c] : 0.f;
+  // logsigmoid(z) = min(z, 0) - log1p(exp(-|z|))
+  g[i] = (fminf(z, 0.f) - log1pf(expf(-fabsf(z)))) * inv_tau;
+}
+
+MS_API int ms_gla_decay(const float* u, int ldu, const void* w2, int w_dtype, const float* b2, int rank, float tau, float* g, int tokens,
+                        int n, cudaStream_t stream) {
+  if (tokens == 0) return 0;
+  MS_REQUIRE(tokens > 0 && n > 0 && rank > 0 && ldu >= rank && tau > 0.f, "gla_decay: bad arguments tokens=%d n=%d rank=%d tau=%g", tokens, n,
+             rank, tau);
+  const size_t total = (size_t)tokens * n;
+  const unsigned blocks = (unsigned)((total + 255) / 256);
+  if (w_dtype == MS_F32)
+    MS_LAUNCH_RESULT("gla_decay", ms_launch(gla_decay_kernel<float>, dim3(blocks), dim3(256), 0, stream, 1, true, u, ldu, (const float*)w2, b2,
+                                            rank, 1.f / tau, g, n, total));
+  else if (w_dtype == MS_BF16)
+    MS_LAUNCH_RESULT("gla_decay", ms_launch(gla_decay_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, 1, true, u, ldu,
+                                            (const __nv_bfloat16*)w2, b2, rank, 1.f / tau, g, n, total));
+  else
+    MS_REQUIRE(false, "gla_decay: unknown weight dtype %d", w_dtype);
+  return 0;
+}
+
+// q, k, v: float32 rows of one product, row stride ld, at column offsets q_off, k_off, v_off; within each, head h begins at
+// h*dk (q, k) or h*dv (v).  g: float32 [T, heads*dk].  state: float32 [slots, heads, dk, dv].  o: float32 [T, heads*dv].
+template <int KPT>
+__global__ void __launch_bounds__(GLA_COLS * GLA_GROUPS)
+gla_scan_kernel(const float* __restrict__ proj, int ld, int q_off, int k_off, int v_off, const float* __restrict__ g, float q_scale,
+                float* __restrict__ state, const int* __restrict__ cu_tokens, const int* __restrict__ state_slots,
+                const int* __restrict__ slot_of_token, float* __restrict__ o, int heads, int dk, int dv) {
+  constexpr int KP = KPT * GLA_GROUPS;  // key rows, padded
+  __shared__ __align__(16) float q_s[GLA_TB][KP], k_s[GLA_TB][KP], a_s[GLA_TB][KP];
+  __shared__ float v_s[GLA_TB][GLA_COLS];
+  __shared__ float part[GLA_TB][GLA_GROUPS][GLA_COLS];
+  ms_pdl_trigger();
+  ms_pdl_wait();
+  const int seq = blockIdx.z, h = blockIdx.y, c0 = blockIdx.x * GLA_COLS;
+  const int row0 = cu_tokens[seq], rows = cu_tokens[seq + 1] - row0;
+  if (rows <= 0 || slot_of_token[row0] < 0) return;  // a sequence of no rows, or rows of no request
+  const int slot = state_slots[seq];
+  const int c = threadIdx.x % GLA_COLS, grp = threadIdx.x / GLA_COLS;
+  const int col = c0 + c;
+  const bool live = col < dv;
+  float* st = state + (((size_t)slot * heads + h) * dk) * dv;
+  float s[KPT];
+#pragma unroll
+  for (int i = 0; i < KPT; ++i) {
+    const int r = grp * KPT + i;
+    s[i] = (live && r < dk) ? st[(size_t)r * dv + col] : 0.f;
+  }
+  for (int t0 = 0; t0 < rows; t0 += GLA_TB) {
+    const int nt = min(GLA_TB, rows - t0);
+    __syncthreads();  // the batch before has been read
+    for (int e = threadIdx.x; e < nt * KP; e += blockDim.x) {
+      const int tb = e / KP, r = e - tb * KP;
+      const size_t t = (size_t)(row0 + t0 + tb);
+      const bool in = r < dk;
+      q_s[tb][r] = in ? proj[t * ld + q_off + h * dk + r] * q_scale : 0.f;
+      k_s[tb][r] = in ? proj[t * ld + k_off + h * dk + r] : 0.f;
+      a_s[tb][r] = in ? expf(g[t * ((size_t)heads * dk) + h * dk + r]) : 1.f;
+    }
+    for (int e = threadIdx.x; e < nt * GLA_COLS; e += blockDim.x) {
+      const int tb = e / GLA_COLS, cc = e - tb * GLA_COLS;
+      v_s[tb][cc] = (c0 + cc < dv) ? proj[(size_t)(row0 + t0 + tb) * ld + v_off + h * dv + c0 + cc] : 0.f;
+    }
+    __syncthreads();
+    for (int tb = 0; tb < nt; ++tb) {
+      const float v = v_s[tb][c];
+      float acc = 0.f;
+#pragma unroll
+      for (int i = 0; i < KPT; i += 2) {  // (KPT is even)
+        const float2 a = *reinterpret_cast<const float2*>(&a_s[tb][grp * KPT + i]);
+        const float2 k = *reinterpret_cast<const float2*>(&k_s[tb][grp * KPT + i]);
+        const float2 q = *reinterpret_cast<const float2*>(&q_s[tb][grp * KPT + i]);
+        s[i] = fmaf(a.x, s[i], k.x * v);
+        s[i + 1] = fmaf(a.y, s[i + 1], k.y * v);
+        acc = fmaf(s[i], q.x, acc);
+        acc = fmaf(s[i + 1], q.y, acc);
+      }
+      part[tb][grp][c] = acc;
+    }
+    __syncthreads();
+    for (int tb = grp; tb < nt; tb += GLA_GROUPS) {
+      float sum = 0.f;
+#pragma unroll
+      for (int gi = 0; gi < GLA_GROUPS; ++gi) sum += part[tb][gi][c];
+      if (live) o[(size_t)(row0 + t0 + tb) * ((size_t)heads * dv) + h * dv + col] = sum;
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < KPT; ++i) {
+    const int r = grp * KPT + i;
+    if (live && r < dk) st[(size_t)r * dv + col] = s[i];
+  }
+}
+
+MS_API int ms_gla_scan(const float* proj, int ld, int q_off, int k_off, int v_off, const float* g, float q_scale, float* state,
+                       const int* cu_tokens, const int* state_slots, const int* slot_of_token, float* o, int seqs, int heads, int dk, int dv,
+                       cudaStream_t stream) {
+  if (seqs == 0) return 0;
+  MS_REQUIRE(seqs > 0 && heads > 0 && dk > 0 && dv > 0, "gla_scan: bad sizes seqs=%d heads=%d dk=%d dv=%d", seqs, heads, dk, dv);
+  MS_REQUIRE(dk <= 32 * GLA_GROUPS, "gla_scan: %d key channels a head are more than the kernel covers (%d)", dk, 32 * GLA_GROUPS);
+  MS_REQUIRE(seqs <= 65535 && heads <= 65535, "gla_scan: too many sequences or heads for one launch");
+  const dim3 grid((dv + GLA_COLS - 1) / GLA_COLS, heads, seqs), block(GLA_COLS * GLA_GROUPS);
+  const int kpt = (dk + GLA_GROUPS - 1) / GLA_GROUPS;
+#define MS_GLA_GO(K)                                                                                                                 \
+  MS_LAUNCH_RESULT("gla_scan", ms_launch(gla_scan_kernel<K>, grid, block, 0, stream, 1, true, proj, ld, q_off, k_off, v_off, g, q_scale, \
+                                         state, cu_tokens, state_slots, slot_of_token, o, heads, dk, dv))
+  if (kpt <= 2) MS_GLA_GO(2);
+  else if (kpt <= 4) MS_GLA_GO(4);
+  else if (kpt <= 6) MS_GLA_GO(6);
+  else if (kpt <= 8) MS_GLA_GO(8);
+  else if (kpt <= 12) MS_GLA_GO(12);
+  else if (kpt <= 16) MS_GLA_GO(16);
+  else if (kpt <= 24) MS_GLA_GO(24);
+  else MS_GLA_GO(32);
+#undef MS_GLA_GO
+  return 0;
+}
+
+template <typename TO>
+__global__ void __launch_bounds__(128)
+gla_output_kernel(const float* __restrict__ o, const float* __restrict__ gate, int ldg, const float* __restrict__ w, float eps,
+                  TO* __restrict__ out, int heads, int dv, int items) {
+  ms_pdl_trigger();
+  ms_pdl_wait();
+  const int lane = threadIdx.x & 31;
+  const int item = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (item >= items) return;
+  const int t = item / heads, h = item - t * heads;
+  const float* x = o + ((size_t)t * heads + h) * dv;
+  float ss = 0.f;
+  for (int d = lane; d < dv; d += 32) ss += x[d] * x[d];
+  ss = ms_warp_sum(ss);
+  const float inv = rsqrtf(ss / (float)dv + eps);
+  const float* gr = gate ? gate + (size_t)t * ldg + (size_t)h * dv : nullptr;
+  for (int d = lane; d < dv; d += 32) {
+    float y = x[d] * inv * (w ? w[d] : 1.f);
+    if (gr) {
+      const float z = gr[d];
+      y *= z / (1.f + expf(-z));
+    }
+    out[((size_t)t * heads + h) * dv + d] = ms_from_float<TO>(y);
+  }
+}
+
+// o float32 [T, heads*dv]; gate float32 rows with stride ldg (the gate's columns begin at the pointer), or null; w float32 [dv].
+MS_API int ms_gla_output(const float* o, const float* gate, int ldg, const float* w, float eps, void* out, int out_dtype, int tokens,
+                         int heads, int dv, cudaStream_t stream) {
+  if (tokens == 0) return 0;
+  MS_REQUIRE(tokens > 0 && heads > 0 && dv > 0 && (gate == nullptr || ldg >= heads * dv), "gla_output: bad sizes");
+  const int items = tokens * heads;
+  const dim3 grid((items + 3) / 4), block(128);
+  if (out_dtype == MS_F32)
+    MS_LAUNCH_RESULT("gla_output", ms_launch(gla_output_kernel<float>, grid, block, 0, stream, 1, true, o, gate, ldg, w, eps, (float*)out, heads,
+                                             dv, items));
+  else if (out_dtype == MS_BF16)
+    MS_LAUNCH_RESULT("gla_output", ms_launch(gla_output_kernel<__nv_bfloat16>, grid, block, 0, stream, 1, true, o, gate, ldg, w, eps,
+                                             (__nv_bfloat16*)out, heads, dv, items));
+  else
+    MS_REQUIRE(false, "gla_output: unknown out dtype %d", out_dtype);
+  return 0;
+}

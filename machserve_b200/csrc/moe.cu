@@ -1,0 +1,179 @@
+// A routed feed-forward (mixture of experts): the router's choice, and the experts' products for (token, expert) pairs.
+//
+//   route:    of a token's E router logits (float32) the `top` largest are chosen (the lower index wins a tie); their
+//             weights are the softmax over the chosen logits only.  ids int32 [T, top], weights float32 [T, top], in
+//             descending order of the logits.  One warp a token.
+//   gate_up:  h[p, n] = act(Wg[e_p][n, :] . x[t_p, :]) * (Wu[e_p][n, :] . x[t_p, :]) for pair p = (token t_p, its j-th expert e_p)
+//   down:     y[t, n] = sum_j weight[t, j] * (Wd[e_(t,j)][n, :] . h[(t, j), :]), j ascending
+// The pair kernels stream the chosen experts' weights once per pair: what decoding rows want (a token reads only
+// its experts) and what the 32-bit path uses for every step: each output is a chain of float32 sums whose order
+// depends on the sizes alone, so a token's result does not depend on the batch.  Expert weights are stacked:
+// Wg, Wu [E, ff, d], Wd [E, d, ff].  Rows of no request (slot < 0) are skipped and get zeros.
+#include "launch.cuh"
+
+__global__ void __launch_bounds__(128)
+moe_route_kernel(const float* __restrict__ logits, int experts, int top, int* __restrict__ ids, float* __restrict__ weights, int tokens) {
+  ms_pdl_trigger();
+  ms_pdl_wait();
+  const int lane = threadIdx.x & 31;
+  const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (t >= tokens) return;
+  const float* z = logits + (size_t)t * experts;
+  // each lane's logits are re-read per round; an expert already chosen is passed over by comparing with the last choice
+  float last_v = INFINITY;
+  int last_i = -1;
+  float first_v = 0.f, sum = 0.f;
+  for (int j = 0; j < top; ++j) {
+    float best = -INFINITY;
+    int best_i = 0x7fffffff;
+    for (int e = lane; e < experts; e += 32) {
+      const float v = z[e];
+      // after (last_v, last_i) in the order: larger value first, lower index first among equals
+      const bool after = v < last_v || (v == last_v && e > last_i);
+      if (after && (v > best || (v == best && e < best_i))) {
+        best = v;
+        best_i = e;
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
+      if (ov > best || (ov == best && oi < best_i)) {
+        best = ov;
+        best_i = oi;
+      }
+    }
+    if (j == 0) first_v = best;
+    const float w = expf(best - first_v);  // the first is the largest
+    sum += w;
+    if (lane == 0) {
+      ids[(size_t)t * top + j] = best_i;
+      weights[(size_t)t * top + j] = w;
+    }
+    last_v = best;
+    last_i = best_i;
+  }
+  __syncwarp();
+  if (lane == 0)
+    for (int j = 0; j < top; ++j) weights[(size_t)t * top + j] /= sum;
+}
+
+MS_API int ms_moe_route(const float* logits, int experts, int top, int* ids, float* weights, int tokens, cudaStream_t stream) {
+  if (tokens == 0) return 0;
+  MS_REQUIRE(tokens > 0 && experts > 0 && top > 0 && top <= experts, "moe_route: bad arguments tokens=%d experts=%d top=%d", tokens, experts, top);
+  MS_LAUNCH_RESULT("moe_route", ms_launch(moe_route_kernel, dim3((tokens + 3) / 4), dim3(128), 0, stream, 1, true, logits, experts, top, ids,
+                                          weights, tokens));
+  return 0;
+}
+
+__device__ __forceinline__ float moe_act(float g, int act) {
+  if (act == 0) return g / (1.f + expf(-g));
+  return 0.5f * g * (1.f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
+}
+
+#define MOE_WARPS 8
+
+// grid (ceil(ff / MOE_WARPS), pairs); a warp an output column; x row of the pair's token in shared memory as float32
+template <typename T>
+__global__ void __launch_bounds__(MOE_WARPS * 32)
+moe_gate_up_pairs_kernel(const T* __restrict__ x, const T* __restrict__ wg, const T* __restrict__ wu, const int* __restrict__ ids,
+                         const int* __restrict__ slots, T* __restrict__ h, int top, int d, int ff, int experts, int act) {
+  extern __shared__ float moe_x[];
+  ms_pdl_trigger();
+  ms_pdl_wait();
+  const int pair = blockIdx.y, t = pair / top;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int n = blockIdx.x * MOE_WARPS + warp;
+  if (slots[t] < 0) {
+    if (n < ff && lane == 0) h[(size_t)pair * ff + n] = ms_from_float<T>(0.f);
+    return;
+  }
+  for (int c = threadIdx.x; c < d; c += blockDim.x) moe_x[c] = ms_to_float(x[(size_t)t * d + c]);
+  __syncthreads();
+  if (n >= ff) return;
+  int e = ids[pair];
+  e = e < 0 ? 0 : (e >= experts ? experts - 1 : e);
+  const T* g = wg + ((size_t)e * ff + n) * d;
+  const T* u = wu + ((size_t)e * ff + n) * d;
+  float sg = 0.f, su = 0.f;
+  for (int c = lane; c < d; c += 32) {
+    const float xv = moe_x[c];
+    sg = fmaf(ms_to_float(g[c]), xv, sg);
+    su = fmaf(ms_to_float(u[c]), xv, su);
+  }
+  sg = ms_warp_sum(sg);
+  su = ms_warp_sum(su);
+  if (lane == 0) h[(size_t)pair * ff + n] = ms_from_float<T>(moe_act(sg, act) * su);
+}
+
+// grid (ceil(d / MOE_WARPS), tokens); a warp an output column, the token's experts in turn
+template <typename T>
+__global__ void __launch_bounds__(MOE_WARPS * 32)
+moe_down_pairs_kernel(const T* __restrict__ h, const T* __restrict__ wd, const int* __restrict__ ids, const float* __restrict__ weights,
+                      const int* __restrict__ slots, float* __restrict__ y, int top, int d, int ff, int experts) {
+  extern __shared__ float moe_h[];  // [top][ff]
+  ms_pdl_trigger();
+  ms_pdl_wait();
+  const int t = blockIdx.y;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int n = blockIdx.x * MOE_WARPS + warp;
+  if (slots[t] < 0) {
+    if (n < d && lane == 0) y[(size_t)t * d + n] = 0.f;
+    return;
+  }
+  for (int c = threadIdx.x; c < top * ff; c += blockDim.x) moe_h[c] = ms_to_float(h[(size_t)t * top * ff + c]);
+  __syncthreads();
+  if (n >= d) return;
+  float total = 0.f;
+  for (int j = 0; j < top; ++j) {
+    int e = ids[(size_t)t * top + j];
+    e = e < 0 ? 0 : (e >= experts ? experts - 1 : e);
+    const T* w = wd + ((size_t)e * d + n) * ff;
+    const float* hj = moe_h + (size_t)j * ff;
+    float s = 0.f;
+    for (int c = lane; c < ff; c += 32) s = fmaf(ms_to_float(w[c]), hj[c], s);
+    s = ms_warp_sum(s);
+    total = fmaf(weights[(size_t)t * top + j], s, total);
+  }
+  if (lane == 0) y[(size_t)t * d + n] = total;
+}
+
+// x [T, d], h [T*top, ff] in the weights' type (dtype); y float32 [T, d].
+MS_API int ms_moe_gate_up_pairs(const void* x, const void* wg, const void* wu, const int* ids, const int* slots, void* h, int dtype,
+                                int tokens, int top, int d, int ff, int experts, int act, cudaStream_t stream) {
+  if (tokens == 0) return 0;
+  MS_REQUIRE(tokens > 0 && top > 0 && d > 0 && ff > 0 && experts > 0 && (act == 0 || act == 1), "moe_gate_up_pairs: bad arguments");
+  MS_REQUIRE((long long)tokens * top <= 65535, "moe_gate_up_pairs: %d pairs are more than one launch takes", tokens * top);
+  MS_REQUIRE((size_t)d * 4 <= 48 * 1024, "moe_gate_up_pairs: rows of %d are too wide", d);
+  const dim3 grid((ff + MOE_WARPS - 1) / MOE_WARPS, tokens * top), block(MOE_WARPS * 32);
+  if (dtype == MS_F32)
+    MS_LAUNCH_RESULT("moe_gate_up_pairs", ms_launch(moe_gate_up_pairs_kernel<float>, grid, block, (size_t)d * 4, stream, 1, true, (const float*)x,
+                                                    (const float*)wg, (const float*)wu, ids, slots, (float*)h, top, d, ff, experts, act));
+  else if (dtype == MS_BF16)
+    MS_LAUNCH_RESULT("moe_gate_up_pairs",
+                     ms_launch(moe_gate_up_pairs_kernel<__nv_bfloat16>, grid, block, (size_t)d * 4, stream, 1, true, (const __nv_bfloat16*)x,
+                               (const __nv_bfloat16*)wg, (const __nv_bfloat16*)wu, ids, slots, (__nv_bfloat16*)h, top, d, ff, experts, act));
+  else
+    MS_REQUIRE(false, "moe_gate_up_pairs: unknown dtype %d", dtype);
+  return 0;
+}
+
+MS_API int ms_moe_down_pairs(const void* h, const void* wd, const int* ids, const float* weights, const int* slots, float* y, int dtype,
+                             int tokens, int top, int d, int ff, int experts, cudaStream_t stream) {
+  if (tokens == 0) return 0;
+  MS_REQUIRE(tokens > 0 && top > 0 && d > 0 && ff > 0 && experts > 0, "moe_down_pairs: bad arguments");
+  MS_REQUIRE(tokens <= 65535, "moe_down_pairs: %d tokens are more than one launch takes", tokens);
+  const size_t smem = (size_t)top * ff * 4;
+  MS_REQUIRE(smem <= 48 * 1024, "moe_down_pairs: %d experts of %d a token need %zu bytes of shared memory", top, ff, smem);
+  const dim3 grid((d + MOE_WARPS - 1) / MOE_WARPS, tokens), block(MOE_WARPS * 32);
+  if (dtype == MS_F32)
+    MS_LAUNCH_RESULT("moe_down_pairs", ms_launch(moe_down_pairs_kernel<float>, grid, block, smem, stream, 1, true, (const float*)h,
+                                                 (const float*)wd, ids, weights, slots, y, top, d, ff, experts));
+  else if (dtype == MS_BF16)
+    MS_LAUNCH_RESULT("moe_down_pairs", ms_launch(moe_down_pairs_kernel<__nv_bfloat16>, grid, block, smem, stream, 1, true,
+                                                 (const __nv_bfloat16*)h, (const __nv_bfloat16*)wd, ids, weights, slots, y, top, d, ff, experts));
+  else
+    MS_REQUIRE(false, "moe_down_pairs: unknown dtype %d", dtype);
+  return 0;
+}

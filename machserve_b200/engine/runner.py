@@ -519,12 +519,18 @@ class ModelRunner:
         views, plans = self._stage_decode(entries, b, length)
         key = (b, length)
         if key not in self._graphs:
+            # The first step of a shape runs plainly (which sizes the scratch memory and loads every kernel) and its
+            # result is the step's; the graph is then recorded for the steps to come, not run: a step must run once,
+            # since a mixer with a recurrent state advances that state every time it runs.
             ctx = self._context(views, b, b, b, plans, 1, length)
-            self.model.forward(ctx, self.bindings)  # sizes the scratch memory and loads every kernel
+            logits = self.model.forward(ctx, self.bindings)
             torch.cuda.current_stream().synchronize()
             before = ops.launches()
-            graph, logits = self._capture(lambda: self.model.forward(ctx, self.bindings))
-            self._graphs[key] = (graph, logits, ops.launches() - before)
+            graph, captured = self._capture(lambda: self.model.forward(ctx, self.bindings))
+            self._graphs[key] = (graph, captured, ops.launches() - before)
+            if captured.data_ptr() != logits.data_ptr():  # (the scratch memory grew under the capture)
+                logits = logits.clone()
+            return logits[: len(entries)]
         graph, logits, launches = self._graphs[key]
         graph.replay()
         ops.count_launches(launches)

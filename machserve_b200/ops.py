@@ -75,6 +75,18 @@ class _Signatures:
     ms_sigmoid_gate_mul = [P, I, P, I, P, I, I, I, P]
     ms_qk_norm_store = [P, I, P, P, F, F, I, P, P, P, I, I, I, P, P, P, P, I, I, I, I, I, I, I, P]
     ms_latent_encode = [P, I, I, P, F, P, I, I, P, P, P, I, I, I, P, P, I, P, I, I, I, I, I, I, I, P]
+    ms_embed_scaled_pos = [P, I, P, P, P, P, I, I, I, I, F, P]
+    ms_add_streams_rmsnorm = [P, P, I, P, I, P, P, P, P, I, P, I, I, F, P]
+    ms_gated_act_mul = [P, I, P, I, I, I, I, P]
+    ms_head_norm_store = [P, I, P, P, F, I, P, P, P, I, I, I, P, P, P, P, I, I, I, I, I, I, I, I, P]
+    ms_attention_wide_scored = [P, P, P, P, I, P, P, P, P, I, I, I, I, I, I, I, I, I, I, F, F, P, I, I, I, P]
+    ms_attention_wide_mma_scored = [P, P, P, P, P, P, P, P, I, I, P, P, I, I, I, I, I, I, I, I, I, F, I, P, F, P, I, I, P]
+    ms_gla_decay = [P, I, P, I, P, I, F, P, I, I, P]
+    ms_gla_scan = [P, I, I, I, I, P, F, P, P, P, P, P, I, I, I, I, P]
+    ms_gla_output = [P, P, I, P, F, P, I, I, I, I, P]
+    ms_moe_route = [P, I, I, P, P, I, P]
+    ms_moe_gate_up_pairs = [P, P, P, P, P, P, I, I, I, I, I, I, I, P]
+    ms_moe_down_pairs = [P, P, P, P, P, P, I, I, I, I, I, I, P]
     ms_attention_wide = [P, P, P, P, I, P, P, P, P, I, I, I, I, I, I, I, I, I, I, F, I, P]
     ms_attention_wide_mma = [P, P, P, P, P, P, P, P, I, I, P, P, I, I, I, I, I, I, I, I, I, F, I, P, P]
     ms_rope_kv_store = [P, I, I, P, P, P, P, I, I, P, I, I, P, P, P, I, I, I, I, I, I, P]
@@ -995,7 +1007,7 @@ def latent_encode(proj, kv_off, w_latent, eps, cos_sin, rot, positions, slot_of_
 
 
 def attention_wide(q, k_pages, v_pages, out, sinks, positions, slot_of_token, block_table, num_heads: int, num_kv_heads: int,
-                   dk: int, dv: int, window: Optional[int], scale: float, share_rows: bool = False):
+                   dk: int, dv: int, window: Optional[int], scale: float, share_rows: bool = False, score: Optional["ScoreExtras"] = None):
     """The exact paged attention for keys and values of different widths, with an optional sink per head in the
     softmax's denominator.  q float32 [T, Hq*dk]; k pages [pages, Hkv, page, dk]; v pages [pages, Hkv, page, vw] of which
     the first dv columns are the values (the same array as the keys for a latent cache); out [T, Hq*dv] in the cache's
@@ -1008,11 +1020,35 @@ def attention_wide(q, k_pages, v_pages, out, sinks, positions, slot_of_token, bl
           and v_pages.shape[3] >= dv, "attention_wide: bad page shapes")
     _need(sinks is None or (sinks.dtype == torch.float32 and sinks.numel() == num_heads), "attention_wide: bad sinks")
     _need(block_table.dtype == torch.int32 and block_table.is_contiguous(), "attention_wide: bad block table")
+    if score is not None:
+        _check(lib().ms_attention_wide_scored(
+            _ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(out), _code(k_pages), _ptr(sinks), _ptr(positions), _ptr(slot_of_token),
+            _ptr(block_table), block_table.shape[1], k_pages.shape[0], tokens, num_heads, num_kv_heads, dk, dv, v_pages.shape[3],
+            k_pages.shape[2], int(window or 0), float(scale), *score.args(num_heads), int(share_rows), _stream()), "attention_wide")
+        return out
     _check(lib().ms_attention_wide(
         _ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(out), _code(k_pages), _ptr(sinks), _ptr(positions), _ptr(slot_of_token),
         _ptr(block_table), block_table.shape[1], k_pages.shape[0], tokens, num_heads, num_kv_heads, dk, dv, v_pages.shape[3],
         k_pages.shape[2], int(window or 0), float(scale), int(share_rows), _stream()), "attention_wide")
     return out
+
+
+class ScoreExtras:
+    """What the wide attention kernels may apply between the scaled score and the softmax, and a mask by chunks:
+    `softcap` (score <- softcap * tanh(score / softcap); None or 0: none), `dist_bias` (float32 [heads, L]: the bias of head
+    h at distance i - j is dist_bias[h, min(i - j, L - 1)], added after the cap and not scaled; None: none), `chunk` (position
+    i sees the keys j <= i with j // chunk == i // chunk only; None or 0: every earlier key, or the window)."""
+
+    def __init__(self, softcap=None, dist_bias: Optional[torch.Tensor] = None, chunk=None):
+        self.softcap, self.dist_bias, self.chunk = float(softcap or 0.0), dist_bias, int(chunk or 0)
+        _need(self.softcap >= 0.0 and self.chunk >= 0, "ScoreExtras: a negative cap or chunk")
+        _need(dist_bias is None or (dist_bias.dtype == torch.float32 and dist_bias.dim() == 2 and dist_bias.is_contiguous()
+                                    and dist_bias.shape[1] > 0), "ScoreExtras: the distance bias must be float32 [heads, L]")
+
+    def args(self, num_heads: int):
+        b = self.dist_bias
+        _need(b is None or b.shape[0] == num_heads, "ScoreExtras: the distance bias has another number of heads")
+        return (c_float(self.softcap), _ptr(b), int(b.shape[1]) if b is not None else 0, self.chunk)
 
 
 def attention_wide_mma_supports(dk: int, dv: int, vw: int, separate_v: bool) -> bool:
@@ -1036,7 +1072,7 @@ def attention_wide_mma_scratch_words(items: int, dv: int, splits: int) -> int:
 
 def attention_wide_mma(q, k_pages, v_pages, out, sinks, positions, slot_of_token, block_table, unit_row0, unit_rows, units: int,
                        heads: bool, num_heads: int, num_kv_heads: int, dk: int, dv: int, window: Optional[int], scale: float,
-                       splits: int = 1, scratch: Optional[torch.Tensor] = None):
+                       splits: int = 1, scratch: Optional[torch.Tensor] = None, score: Optional[ScoreExtras] = None):
     """attention_wide on the tensor cores (mma.sync, bfloat16 cache and output, float32 queries and softmax).
     heads False: `units` tiles of at most attention_wide_mma_tile_rows(dv) consecutive rows of one sequence, tile u = rows
     unit_row0[u] .. + unit_rows[u].
@@ -1055,11 +1091,18 @@ def attention_wide_mma(q, k_pages, v_pages, out, sinks, positions, slot_of_token
         groups = num_heads // num_kv_heads
         need = attention_wide_mma_scratch_words(units * num_kv_heads * (-(-groups // 16)), dv, splits)
         _need(scratch is not None and scratch.dtype == torch.float32 and scratch.numel() >= need, "attention_wide_mma: scratch too small")
-    _check(lib().ms_attention_wide_mma(
-        _ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(out), _ptr(sinks), _ptr(positions), _ptr(slot_of_token), _ptr(block_table),
-        block_table.shape[1], k_pages.shape[0], _ptr(unit_row0), _ptr(unit_rows), int(units), int(heads), num_heads, num_kv_heads,
-        dk, dv, v_pages.shape[3], k_pages.shape[2], int(window or 0), float(scale), int(splits), _ptr(scratch), _stream()),
-        "attention_wide_mma")
+    if score is not None:
+        _check(lib().ms_attention_wide_mma_scored(
+            _ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(out), _ptr(sinks), _ptr(positions), _ptr(slot_of_token), _ptr(block_table),
+            block_table.shape[1], k_pages.shape[0], _ptr(unit_row0), _ptr(unit_rows), int(units), int(heads), num_heads, num_kv_heads,
+            dk, dv, v_pages.shape[3], k_pages.shape[2], int(window or 0), float(scale), int(splits), _ptr(scratch),
+            *score.args(num_heads), _stream()), "attention_wide_mma")
+    else:
+        _check(lib().ms_attention_wide_mma(
+            _ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(out), _ptr(sinks), _ptr(positions), _ptr(slot_of_token), _ptr(block_table),
+            block_table.shape[1], k_pages.shape[0], _ptr(unit_row0), _ptr(unit_rows), int(units), int(heads), num_heads, num_kv_heads,
+            dk, dv, v_pages.shape[3], k_pages.shape[2], int(window or 0), float(scale), int(splits), _ptr(scratch), _stream()),
+            "attention_wide_mma")
     if splits > 1:
         count_launches(1)  # the merge of the splits
     return out
@@ -1083,6 +1126,187 @@ def linear_heads(x, w, out):
     else:
         torch.bmm(x.transpose(0, 1), w.transpose(1, 2), out_dtype=torch.float32, out=out.transpose(0, 1))
     return out
+
+
+# ------------------------------------------------- scaled embedding with positions, pair-adding RMS norm, gated activations
+
+
+def embed_scaled_pos(table, ids, positions, pos_table, out, scale: float):
+    """out[r, :] = table[ids[r], :] * scale + pos_table[positions[r], :] in float32.  table [V, d] float32 or bfloat16;
+    pos_table float32 [P, d] or None; ids, positions int32 [R]; out float32 [R, d]."""
+    rows, d = out.shape
+    _need(out.dtype == torch.float32 and out.is_contiguous() and table.is_contiguous() and table.shape[1] == d
+          and ids.dtype == torch.int32 and positions.dtype == torch.int32 and ids.numel() >= rows and positions.numel() >= rows,
+          "embed_scaled_pos: bad arguments")
+    _need(pos_table is None or (pos_table.dtype == torch.float32 and pos_table.is_contiguous() and pos_table.shape[1] == d),
+          "embed_scaled_pos: bad table of positions")
+    _check(lib().ms_embed_scaled_pos(_ptr(table), _code(table), _ptr(ids), _ptr(positions), _ptr(pos_table), _ptr(out), rows, d,
+                                     table.shape[0], pos_table.shape[0] if pos_table is not None else 0, float(scale), _stream()),
+           "embed_scaled_pos")
+    return out
+
+
+def add_streams_rmsnorm(residual, delta_a, delta_b, first, vec, weight, out, eps: float = 0.0, rows=None):
+    """residual += (delta_a + delta_b) + first + vec (each may be None), then, with `weight`, out = residual / rms * weight.
+    With `rows`, output row i comes from input row rows[i] and nothing is written back.  residual, first float32 [T, d];
+    deltas [T, d] float32 or bfloat16; vec, weight float32 [d]; out [n_out, d] float32 or bfloat16 (None without a weight)."""
+    t, d = residual.shape
+    _need(residual.dtype == torch.float32 and residual.is_contiguous(), "add_streams_rmsnorm: bad stream")
+    for dl in (delta_a, delta_b):
+        _need(dl is None or (dl.shape[1] == d and dl.is_contiguous() and dl.shape[0] >= t), "add_streams_rmsnorm: bad delta")
+    _need(first is None or (first.dtype == torch.float32 and first.is_contiguous() and first.shape[1] == d and first.shape[0] >= t),
+          "add_streams_rmsnorm: bad second stream")
+    for v in (vec, weight):
+        _need(v is None or (v.dtype == torch.float32 and v.is_contiguous() and v.numel() == d), "add_streams_rmsnorm: bad vector")
+    if weight is None:
+        _need(out is None and rows is None, "add_streams_rmsnorm: an output without a weight")
+        n_out = t
+    else:
+        _need(out is not None and out.is_contiguous() and out.shape[1] == d, "add_streams_rmsnorm: bad output")
+        n_out = out.shape[0]
+        if rows is None:
+            _need(n_out == t, "add_streams_rmsnorm: out must have the stream's rows")
+        else:
+            _need(rows.dtype == torch.int32 and rows.numel() >= n_out, "add_streams_rmsnorm: bad row list")
+    _check(lib().ms_add_streams_rmsnorm(_ptr(residual), *_delta_args(delta_a), *_delta_args(delta_b), _ptr(first), _ptr(vec), _ptr(weight),
+                                        _ptr(out), _code(out) if out is not None else F32, _ptr(rows), n_out, d, float(eps), _stream()),
+           "add_streams_rmsnorm")
+    return out
+
+
+ACTIVATIONS = {"silu": 0, "gelu_tanh": 1}
+
+
+def gated_act_mul(gate_up, out, activation: str):
+    """out[r, c] = act(gate_up[r, c]) * gate_up[r, inter + c]; act "silu" or "gelu_tanh" (0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3)))),
+    in float32.  gate_up [R, 2*inter], out [R, inter], each float32 or bfloat16."""
+    rows, inter = out.shape
+    _need(activation in ACTIVATIONS, f"gated_act_mul: activation '{activation}' is not known ({', '.join(ACTIVATIONS)})")
+    _need(tuple(gate_up.shape) == (rows, 2 * inter) and gate_up.is_contiguous() and out.is_contiguous(), "gated_act_mul: bad layout")
+    for r0 in range(0, rows, 65535):
+        n = min(65535, rows - r0)
+        _check(lib().ms_gated_act_mul(_ptr(gate_up[r0:]), _code(gate_up), _ptr(out[r0:]), _code(out), n, inter, ACTIVATIONS[activation],
+                                      _stream()), "gated_act_mul")
+    return out
+
+
+def head_norm_store(proj, eps: float, positions, slot_of_token, block_table, q_out, k_pages, v_pages, num_heads: int, num_kv_heads: int,
+                    dk: int, dv: int, v_off: Optional[int], norm: bool = True, wq=None, wk=None, store: bool = True, q_half=None):
+    """Every query head and every key head divided by its own root mean square over dk (eps inside the root; optional
+    weights wq, wk float32 [dk]; `norm` False leaves them as they are); q to q_out (float32 [T, Hq*dk]) and, optionally, to
+    a bfloat16 copy; the normed keys into k_pages; into v_pages the values at column `v_off` of the product, or, `v_off`
+    None, the keys as they were projected (before the norm).  proj float32 [T, >= (Hq + Hkv)*dk (+ Hkv*dv)] = [q | k | v]."""
+    t = q_out.shape[0]
+    _need(proj.dtype == torch.float32 and proj.stride(1) == 1 and q_out.dtype == torch.float32 and q_out.is_contiguous()
+          and q_out.numel() == t * num_heads * dk, "head_norm_store: bad layout")
+    _need(q_half is None or (q_half.dtype == torch.bfloat16 and q_half.is_contiguous() and q_half.numel() == q_out.numel()),
+          "head_norm_store: bad bfloat16 copy of the queries")
+    for w in (wq, wk):
+        _need(w is None or (w.dtype == torch.float32 and w.numel() == dk and w.is_contiguous()), "head_norm_store: bad norm weight")
+    if store:
+        _need(k_pages.is_contiguous() and v_pages.is_contiguous() and k_pages.dtype == v_pages.dtype
+              and tuple(k_pages.shape[1:]) == (num_kv_heads, k_pages.shape[2], dk)
+              and tuple(v_pages.shape[1:]) == (num_kv_heads, k_pages.shape[2], dv), "head_norm_store: bad pages")
+        _need(block_table.dtype == torch.int32 and block_table.is_contiguous(), "head_norm_store: bad block table")
+    _check(lib().ms_head_norm_store(
+        _ptr(proj), proj.stride(0), _ptr(wq), _ptr(wk), float(eps), int(norm), _ptr(positions), _ptr(slot_of_token), _ptr(block_table),
+        block_table.shape[1] if store else 0, k_pages.shape[0] if store else 0, k_pages.shape[2] if store else 0, _ptr(q_out),
+        _ptr(q_half), _ptr(k_pages if store else None), _ptr(v_pages if store else None), _code(k_pages) if store else F32, t,
+        num_heads, num_kv_heads, dk, dv, -1 if v_off is None else int(v_off), int(store), _stream()), "head_norm_store")
+    return q_out
+
+
+# ------------------------------------------------------------------------------------------- gated linear attention
+
+
+def gla_decay(u, w2, b2, tau: float, out):
+    """out[t, n] = logsigmoid(w2[n, :] . u[t, :] + b2[n]) / tau: the logarithm of the decay sigmoid(z)^(1/tau), in float32.
+    u float32 [T, rank] (unit column stride); w2 [n, rank] float32 or bfloat16; b2 float32 [n] or None; out float32 [T, n]."""
+    t, n = out.shape
+    rank = w2.shape[1]
+    _need(u.dtype == torch.float32 and u.stride(1) == 1 and u.shape[1] == rank and out.dtype == torch.float32 and out.is_contiguous()
+          and w2.is_contiguous() and w2.shape[0] == n, "gla_decay: bad layout")
+    _need(b2 is None or (b2.dtype == torch.float32 and b2.numel() == n), "gla_decay: bad bias")
+    _check(lib().ms_gla_decay(_ptr(u), u.stride(0), _ptr(w2), _code(w2), _ptr(b2), rank, float(tau), _ptr(out), t, n, _stream()), "gla_decay")
+    return out
+
+
+def gla_scan(proj, q_off: int, k_off: int, v_off: int, log_decay, q_scale: float, state, cu_tokens, state_slots, slot_of_token, out,
+             seqs: int, heads: int, dk: int, dv: int):
+    """The recurrence S <- diag(exp(g_t)) S + k_t v_t^T, o_t = S^T (q_t * q_scale), per sequence and head, over the rows of the
+    step in order, from and to `state` (float32 [slots, heads, dk, dv]; a sequence's slot is state_slots[s]).
+    proj float32 [T, ld] holds q, k (heads*dk each) and v (heads*dv) at the column offsets; log_decay float32 [T, heads*dk];
+    out float32 [T, heads*dv]; cu_tokens int32 [seqs + 1]; rows whose slot_of_token is negative are passed over."""
+    _need(proj.dtype == torch.float32 and proj.stride(1) == 1 and log_decay.dtype == torch.float32 and log_decay.is_contiguous()
+          and out.dtype == torch.float32 and out.is_contiguous() and state.dtype == torch.float32 and state.is_contiguous(),
+          "gla_scan: bad layout")
+    _need(tuple(state.shape[1:]) == (heads, dk, dv) and log_decay.shape[1] == heads * dk and out.shape[1] == heads * dv,
+          "gla_scan: bad shapes")
+    _need(cu_tokens.numel() >= seqs + 1 and state_slots.numel() >= seqs, "gla_scan: bad sequence lists")
+    _check(lib().ms_gla_scan(_ptr(proj), proj.stride(0), int(q_off), int(k_off), int(v_off), _ptr(log_decay), float(q_scale), _ptr(state),
+                             _ptr(cu_tokens), _ptr(state_slots), _ptr(slot_of_token), _ptr(out), int(seqs), heads, dk, dv, _stream()),
+           "gla_scan")
+    return out
+
+
+def gla_output(o, gate, weight, eps: float, out, heads: int, dv: int):
+    """out = o / rms(o) * weight (per head over dv, eps inside the root) * silu(gate).  o float32 [T, heads*dv]; gate float32
+    [T, heads*dv] with unit column stride (any row stride) or None; weight float32 [dv] or None; out [T, heads*dv]."""
+    t = o.shape[0]
+    _need(o.dtype == torch.float32 and o.is_contiguous() and out.is_contiguous() and o.shape[1] == heads * dv
+          and tuple(out.shape) == tuple(o.shape), "gla_output: bad layout")
+    _need(gate is None or (gate.dtype == torch.float32 and gate.stride(1) == 1 and gate.shape[1] == heads * dv), "gla_output: bad gate")
+    _need(weight is None or (weight.dtype == torch.float32 and weight.numel() == dv), "gla_output: bad weight")
+    _check(lib().ms_gla_output(_ptr(o), _ptr(gate), gate.stride(0) if gate is not None else 0, _ptr(weight), float(eps), _ptr(out),
+                               _code(out), t, heads, dv, _stream()), "gla_output")
+    return out
+
+
+# ------------------------------------------------------------------------------------------------ routed feed-forward
+
+
+def moe_route(logits, top: int, ids, weights):
+    """Of each row's router logits (float32 [T, E]) the `top` largest (the lower index wins a tie), in descending order:
+    ids int32 [T, top], weights float32 [T, top] = the softmax over the chosen logits only."""
+    t, e = logits.shape
+    _need(logits.dtype == torch.float32 and logits.is_contiguous() and ids.dtype == torch.int32 and ids.is_contiguous()
+          and weights.dtype == torch.float32 and weights.is_contiguous() and tuple(ids.shape) == (t, top) and tuple(weights.shape) == (t, top),
+          "moe_route: bad arguments")
+    _check(lib().ms_moe_route(_ptr(logits), e, int(top), _ptr(ids), _ptr(weights), t, _stream()), "moe_route")
+    return ids, weights
+
+
+def moe_gate_up_pairs(x, w_gate, w_up, ids, slot_of_token, h, activation: str):
+    """h[t*top + j, :] = act(w_gate[e] x_t) * (w_up[e] x_t) with e = ids[t, j].  x [T, d]; w_gate, w_up [E, ff, d];
+    h [T*top, ff]; all of one dtype (float32 or bfloat16).  Rows with a negative slot get zeros."""
+    t, d = x.shape
+    experts, ff, _ = w_gate.shape
+    top = ids.shape[1]
+    _need(x.is_contiguous() and w_gate.is_contiguous() and w_up.is_contiguous() and h.is_contiguous() and ids.is_contiguous()
+          and x.dtype == w_gate.dtype == w_up.dtype == h.dtype and tuple(w_up.shape) == (experts, ff, d) and w_gate.shape[2] == d
+          and tuple(h.shape) == (t * top, ff) and ids.dtype == torch.int32 and ids.shape[0] == t, "moe_gate_up_pairs: bad arguments")
+    step = max(1, 65535 // top)
+    for t0 in range(0, t, step):
+        n = min(step, t - t0)
+        _check(lib().ms_moe_gate_up_pairs(_ptr(x[t0:]), _ptr(w_gate), _ptr(w_up), _ptr(ids[t0:]), _ptr(slot_of_token[t0:]), _ptr(h[t0 * top:]),
+                                          _code(x), n, top, d, ff, experts, ACTIVATIONS[activation], _stream()), "moe_gate_up_pairs")
+    return h
+
+
+def moe_down_pairs(h, w_down, ids, weights, slot_of_token, y):
+    """y[t, :] = sum_j weights[t, j] * (w_down[ids[t, j]] h[t*top + j, :]), j ascending, in float32.  h [T*top, ff];
+    w_down [E, d, ff] of h's dtype; y float32 [T, d]."""
+    t, d = y.shape
+    experts, _, ff = w_down.shape
+    top = ids.shape[1]
+    _need(h.is_contiguous() and w_down.is_contiguous() and y.is_contiguous() and y.dtype == torch.float32 and h.dtype == w_down.dtype
+          and tuple(h.shape) == (t * top, ff) and w_down.shape[1] == d and weights.dtype == torch.float32 and weights.is_contiguous()
+          and tuple(weights.shape) == (t, top) and ids.dtype == torch.int32 and ids.is_contiguous(), "moe_down_pairs: bad arguments")
+    for t0 in range(0, t, 65535):
+        n = min(65535, t - t0)
+        _check(lib().ms_moe_down_pairs(_ptr(h[t0 * top:]), _ptr(w_down), _ptr(ids[t0:]), _ptr(weights[t0:]), _ptr(slot_of_token[t0:]),
+                                       _ptr(y[t0:]), _code(h), n, top, d, ff, experts, _stream()), "moe_down_pairs")
+    return y
 
 
 def apply_logit_offsets(logits, row_ptr, tokens, amounts):

@@ -51,11 +51,13 @@ class CachePlane:
 
 @dataclass(frozen=True)
 class PagedCache:
-    """What a mixer keeps per token, in pages: one or more planes, for every token or for the last `window`
-    tokens.  Runs of layers whose needs are equal share a group of pages and one block table per request."""
+    """What a mixer keeps per token, in pages: one or more planes, for every token, for the last `window` tokens, or,
+    with `chunk`, for the tokens of the chunk (positions floor(p / chunk) * chunk and up) that the newest token lies in.
+    Runs of layers whose needs are equal share a group of pages and one block table per request."""
 
     planes: Tuple[CachePlane, ...]
     window: Optional[int] = None
+    chunk: Optional[int] = None
 
     def elements_per_token(self) -> int:
         return sum(p.elements_per_token() for p in self.planes)

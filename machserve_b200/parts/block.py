@@ -51,7 +51,8 @@ class ParallelBlock(Block):
     """x += mixer(norm1(x)) + feed_forward(norm2(x)): both norms read the same x, and the two outputs are summed before
     they are added to the stream.  The block hands both on (`DeltaPair`); the next norm adds them in float32.  Two layer
     norms of equal size and eps share their mean and variance and are written by one kernel.  A layer without a
-    feed-forward is x += mixer(norm1(x)).
+    feed-forward is x += mixer(norm1(x)).  A layer with a feed-forward but no norm of its own for it has ONE norm whose
+    output both halves read: x += mixer(norm1(x)) + feed_forward(norm1(x)).
     """
 
     graph_safe = True
@@ -71,10 +72,14 @@ class ParallelBlock(Block):
         if self.feed_forward is None:
             self.mixer_norm.forward(residual, as_delta(pending, pairs), xn)
             return self.mixer.forward(ctx, xn, cache, owns_cache)
-        xf = rt.workspace.get("block.normed_ff", (t, d), rt.dtype)
-        if self.one_kernel:
+        if self.ff_norm is None:  # one norm, read by both halves
+            xf = xn
+            self.mixer_norm.forward(residual, as_delta(pending, pairs), xn)
+        elif self.one_kernel:
+            xf = rt.workspace.get("block.normed_ff", (t, d), rt.dtype)
             self.mixer_norm.forward_both(self.ff_norm, residual, as_delta(pending, pairs), xn, xf)
         else:
+            xf = rt.workspace.get("block.normed_ff", (t, d), rt.dtype)
             self.mixer_norm.forward(residual, as_delta(pending, pairs), xn)
             self.ff_norm.forward(residual, None, xf)
         # The two halves read different rows and share no scratch memory.  In a captured step they run side by side, as

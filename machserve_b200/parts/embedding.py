@@ -33,6 +33,42 @@ class Embedding(TokenEmbedding):
         return ops.embed_gather(self.table, ctx.token_ids, out)
 
 
+@register_embedding("scaled_position_embedding")
+class ScaledPositionEmbedding(TokenEmbedding):
+    """x[r, :] = E[token[r], :] * scale + P[position[r], :] into the float32 residual stream: the table's rows are scaled,
+    the learned position vectors (a table [max_positions, hidden], or none) are not.  A head tied to `tensor` reads the
+    table itself, without the scale.
+
+    params: tensor, vocab_size, hidden_size, scale, positions (tensor name or None), max_positions.
+    """
+
+    graph_safe = True
+
+    def __init__(self, spec):
+        super().__init__(spec)
+        self.name, self.vocab, self.hidden = spec["tensor"], int(spec["vocab_size"]), int(spec["hidden_size"])
+        self.scale = float(spec.get("scale", 1.0))
+        self.positions_name, self.max_positions = spec.get("positions"), int(spec.get("max_positions", 0))
+        if self.positions_name is not None and self.max_positions < 1:
+            raise ValueError("scaled_position_embedding: a table of positions needs max_positions")
+
+    def tensors(self):
+        out = [TensorDecl(self.name, (self.vocab, self.hidden))]
+        if self.positions_name is not None:
+            out.append(TensorDecl(self.positions_name, (self.max_positions, self.hidden), init="bias"))
+        return out
+
+    def bind(self, tensors, rt):
+        super().bind(tensors, rt)
+        self.table = matrix(tensors[self.name], rt)
+        self.pos_table = None
+        if self.positions_name is not None:
+            self.pos_table = tensors[self.positions_name].to(torch.float32).contiguous()
+
+    def forward(self, ctx, out):
+        return ops.embed_scaled_pos(self.table, ctx.token_ids, ctx.positions, self.pos_table, out, self.scale)
+
+
 @register_head("lm_head")
 class LMHead(Head):
     """logits = x . W^T in float32, for the rows that are asked for only (the reference computes

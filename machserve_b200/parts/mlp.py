@@ -1,4 +1,4 @@
-"""The dense gated feed-forwards: SwiGLU, and the clamped gated unit."""
+"""The dense gated feed-forwards: SwiGLU, the clamped gated unit, and the gated unit with a choice of activation."""
 from __future__ import annotations
 
 import torch
@@ -128,5 +128,46 @@ class ClampedGLU(FeedForward):
         ops.linear(x, self.w_gate_up, None, gate_up)
         h = ws.get("ffn.h", (t, self.inter), rt.dtype)
         ops.glu_clamped(gate_up, h, self.limit, self.alpha, self.shift)
+        delta = ws.get("ffn.delta_f32", (t, self.hidden), torch.float32)
+        return ops.linear(h, self.w_down, None, delta)
+
+
+@register_feed_forward("gated_mlp")
+class GatedMLP(FeedForward):
+    """delta = down(act(gate(x)) * up(x)), act "silu" or "gelu_tanh"; no biases.  gate and up are one matrix product over
+    the concatenated weights; the activation is computed in float32; the delta is float32.
+
+    params: prefix, hidden_size, intermediate_size, activation, and the three tensor names under the prefix: gate, up,
+    down (`gate`, `up`, `down` if absent).
+    """
+
+    graph_safe = True
+
+    def __init__(self, spec):
+        super().__init__(spec)
+        self.prefix = spec["prefix"]
+        self.hidden, self.inter = int(spec["hidden_size"]), int(spec["intermediate_size"])
+        self.activation = spec["activation"]
+        if self.activation not in ops.ACTIVATIONS:
+            raise ValueError(f"gated_mlp: activation '{self.activation}' is not known ({', '.join(ops.ACTIVATIONS)})")
+        self.names = tuple(self.prefix + spec.get(k, k) for k in ("gate", "up", "down"))
+
+    def tensors(self):
+        g, u, d = self.names
+        return [TensorDecl(g, (self.inter, self.hidden)), TensorDecl(u, (self.inter, self.hidden)), TensorDecl(d, (self.hidden, self.inter))]
+
+    def bind(self, tensors, rt):
+        super().bind(tensors, rt)
+        g, u, d = self.names
+        self.w_gate_up = matrix(torch.cat([tensors[g], tensors[u]], dim=0), rt)
+        self.w_down = matrix(tensors[d], rt)
+
+    def forward(self, ctx, x):
+        rt, t = self.rt, x.shape[0]
+        ws = rt.workspace
+        gate_up = ws.get("ffn.gate_up", (t, 2 * self.inter), rt.dtype)
+        ops.linear(x, self.w_gate_up, None, gate_up)
+        h = ws.get("ffn.h", (t, self.inter), rt.dtype)
+        ops.gated_act_mul(gate_up, h, self.activation)
         delta = ws.get("ffn.delta_f32", (t, self.hidden), torch.float32)
         return ops.linear(h, self.w_down, None, delta)

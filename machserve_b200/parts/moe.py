@@ -1,0 +1,65 @@
+"""A routed feed-forward: a mixture of small gated feed-forwards of which every token uses a few."""
+from __future__ import annotations
+
+import torch
+
+from .. import ops
+from ..weights.loader import TensorDecl
+from .base import FeedForward, matrix, register_feed_forward, vector_f32
+
+
+@register_feed_forward("routed_experts")
+class RoutedExperts(FeedForward):
+    """Router logits z = Wr x (+ br) in float32; of the `experts` experts the `top` with the largest logits are chosen, their
+    weights are the softmax over the chosen logits only; delta = sum of weight_e * down_e(act(gate_e(x)) * up_e(x)) over
+    the chosen experts; experts have no biases; act "silu" or "gelu_tanh".  The experts' matrices are stacked on the device
+    ([experts, ff, hidden] twice, [experts, hidden, ff]); a token's (token, expert) pairs read the chosen experts' rows only.
+
+    params: prefix, hidden_size, intermediate_size (of one expert), experts, top, activation, router_bias (bool).  Tensors
+    under the prefix: router [experts, hidden], router.b, e<i>.gate, e<i>.up, e<i>.down.
+    """
+
+    graph_safe = True
+
+    def __init__(self, spec):
+        super().__init__(spec)
+        self.prefix = spec["prefix"]
+        self.hidden, self.inter = int(spec["hidden_size"]), int(spec["intermediate_size"])
+        self.experts, self.top = int(spec["experts"]), int(spec["top"])
+        self.activation = spec.get("activation", "silu")
+        self.router_bias = bool(spec.get("router_bias", True))
+        if not 1 <= self.top <= self.experts:
+            raise ValueError(f"routed_experts: {self.top} of {self.experts} experts a token")
+        if self.activation not in ops.ACTIVATIONS:
+            raise ValueError(f"routed_experts: activation '{self.activation}' is not known ({', '.join(ops.ACTIVATIONS)})")
+
+    def tensors(self):
+        p = self.prefix
+        out = [TensorDecl(p + "router", (self.experts, self.hidden))]
+        if self.router_bias:
+            out.append(TensorDecl(p + "router.b", (self.experts,), init="bias"))
+        for e in range(self.experts):
+            out += [TensorDecl(f"{p}e{e}.gate", (self.inter, self.hidden)), TensorDecl(f"{p}e{e}.up", (self.inter, self.hidden)),
+                    TensorDecl(f"{p}e{e}.down", (self.hidden, self.inter))]
+        return out
+
+    def bind(self, tensors, rt):
+        super().bind(tensors, rt)
+        p = self.prefix
+        self.w_router = matrix(tensors[p + "router"], rt)
+        self.b_router = vector_f32(tensors[p + "router.b"]) if self.router_bias else None
+        stack = lambda name: matrix(torch.stack([tensors[f"{p}e{e}.{name}"] for e in range(self.experts)], dim=0), rt)
+        self.w_gate, self.w_up, self.w_down = stack("gate"), stack("up"), stack("down")
+
+    def forward(self, ctx, x):
+        rt, t = self.rt, x.shape[0]
+        ws = rt.workspace
+        logits = ws.get("moe.logits", (t, self.experts), torch.float32)
+        ops.linear(x, self.w_router, self.b_router, logits)
+        ids = ws.get("moe.ids", (t, self.top), torch.int32)
+        weights = ws.get("moe.weights", (t, self.top), torch.float32)
+        ops.moe_route(logits, self.top, ids, weights)
+        h = ws.get("moe.h", (t * self.top, self.inter), rt.dtype)
+        ops.moe_gate_up_pairs(x, self.w_gate, self.w_up, ids, ctx.slot_of_token, h, self.activation)
+        delta = ws.get("ffn.delta_f32", (t, self.hidden), torch.float32)
+        return ops.moe_down_pairs(h, self.w_down, ids, weights, ctx.slot_of_token, delta)

@@ -15,6 +15,7 @@ class RMSNorm(Norm):
     """
 
     graph_safe = True
+    accepts_pairs = True  # a `DeltaPair` is summed and added by a kernel of its own (x + (a + b), float32)
 
     def __init__(self, spec):
         super().__init__(spec)
@@ -28,6 +29,8 @@ class RMSNorm(Norm):
         self.weight = vector_f32(tensors[self.name])
 
     def forward(self, residual, delta, out, rows=None):
+        if isinstance(delta, DeltaPair):
+            return ops.add_streams_rmsnorm(residual, delta.a, delta.b, None, None, self.weight, out, self.eps, rows)
         return ops.add_rmsnorm(residual, as_delta(delta), self.weight, out, self.eps, rows)
 
     def fold_into(self, matrix):

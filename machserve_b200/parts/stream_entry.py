@@ -45,3 +45,35 @@ class MixWithEmbedding(StreamEntry):
         ops.concat_streams(residual, a, b, first, both)
         ops.linear(both, self.weight, self.vector, residual)
         return None
+
+
+@register_stream_entry("add_embedding")
+class AddEmbedding(StreamEntry):
+    """x <- x + x0 + s: the embedding's output is added to the stream (only with `add_first`), then a vector: row `row`
+    of a table [rows, hidden] (one row per pass of a loop over layers).  The pending deltas are added to x first; all
+    in float32, by one kernel.
+
+    params: vectors (tensor name), rows, row, hidden_size, add_first.
+    """
+
+    graph_safe = True
+
+    def __init__(self, spec):
+        super().__init__(spec)
+        self.vectors_name = spec["vectors"]
+        self.rows, self.row, self.hidden = int(spec["rows"]), int(spec["row"]), int(spec["hidden_size"])
+        self.add_first = bool(spec["add_first"])
+        if not 0 <= self.row < self.rows:
+            raise ValueError(f"add_embedding: row {self.row} of {self.rows}")
+
+    def tensors(self):
+        return [TensorDecl(self.vectors_name, (self.rows, self.hidden), init="bias")]
+
+    def bind(self, tensors, rt):
+        super().bind(tensors, rt)
+        self.vector = vector_f32(tensors[self.vectors_name][self.row])
+
+    def forward(self, ctx, residual, pending, first):
+        a, b = (pending.a, pending.b) if isinstance(pending, DeltaPair) else (as_delta(pending), None)
+        ops.add_streams_rmsnorm(residual, a, b, first if self.add_first else None, self.vector, None, None)
+        return None

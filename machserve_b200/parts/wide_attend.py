@@ -118,15 +118,18 @@ def attend_single_cluster(ctx, rt, launch_cache: dict, table, q_half, k_pages, v
 
 
 def attend(ctx, rt, fast: bool, table, q, k_pages, v_pages, out, sinks, hq: int, hkv: int, dk: int, dv: int, window, scale: float,
-           q_half=None, tcgen05: bool = False, cluster=None):
+           q_half=None, tcgen05: bool = False, cluster=None, score=None):
     """Every row of q over its sequence's pages: on the tensor cores when the widths allow it in bfloat16 (decoding rows
     with their key tiles cut into as many runs as fill the GPU, portions in tiles of 64, 32 or 16 rows), else the exact kernel.
     With `q_half` (the queries in bfloat16) the framework's own kernels for keys and values of one width take what they
     cover: `cluster` (a dict for the launch rules' results) sends decoding rows to its cluster kernel, `tcgen05` the
-    portions to its tcgen05 kernel; both add the sinks themselves."""
+    portions to its tcgen05 kernel; both add the sinks themselves.  `score` (`ops.ScoreExtras`: a soft cap, a bias by head
+    and distance, a mask by chunks) is applied by the exact and the mma.sync kernels; the other two do not have it."""
+    if score is not None and (tcgen05 or cluster is not None):
+        raise ValueError("the tcgen05 and cluster attention kernels have no soft cap, distance bias or chunks")
     if not fast:
         return ops.attention_wide(q, k_pages, v_pages, out, sinks, ctx.positions, ctx.slot_of_token, table, hq, hkv,
-                                  dk, dv, window, scale, share_rows=ctx.max_query_len > 1)
+                                  dk, dv, window, scale, share_rows=ctx.max_query_len > 1, score=score)
     work = ctx.work[PLAN]
     tile = ops.attention_wide_mma_tile_rows(dv)
     singles, tiles = work.sizes["single_rows"], work.sizes[f"tile{tile}_row0"]
@@ -137,18 +140,20 @@ def attend(ctx, rt, fast: bool, table, q, k_pages, v_pages, out, sinks, hq: int,
         keys = work.shape[0] * CONTEXT_BUCKET
         if window:
             keys = min(keys, window + 63)
+        if score is not None and score.chunk:
+            keys = min(keys, score.chunk + 63)
         splits = max(1, min(BLOCKS_PER_SM * rt.sm_count // items, -(-keys // 64), 32))
         scratch = None
         if splits > 1:
             scratch = rt.workspace.get("wide_attend.splits", (ops.attention_wide_mma_scratch_words(items, dv, splits),), torch.float32)
         rows = None if tiles == 0 and singles == q.shape[0] else work.lists["single_rows"]
         ops.attention_wide_mma(q, k_pages, v_pages, out, sinks, ctx.positions, ctx.slot_of_token, table, rows, None, singles, True,
-                               hq, hkv, dk, dv, window, scale, splits, scratch)
+                               hq, hkv, dk, dv, window, scale, splits, scratch, score=score)
     if tcgen05 and q_half is not None:  # portions on the tcgen05 kernel (the part has made sure that it covers the sizes)
         attend_portions_tcgen05(ctx, rt, table, q_half, k_pages, v_pages, out, sinks, hq, hkv, dk, window, scale)
     elif tiles:
         ops.attention_wide_mma(q, k_pages, v_pages, out, sinks, ctx.positions, ctx.slot_of_token, table, work.lists[f"tile{tile}_row0"],
-                               work.lists[f"tile{tile}_rows"], tiles, False, hq, hkv, dk, dv, window, scale)
+                               work.lists[f"tile{tile}_rows"], tiles, False, hq, hkv, dk, dv, window, scale, score=score)
     return out
 
 
