@@ -31,6 +31,9 @@ latent attention, clamped gated feed-forward) at the layer sizes of the three Qw
 at the same sizes: decode at `--batch` and `--context`, one prompt of `--prefill` tokens, and the design's kernels
 alone beside the like kernels of the dense decoder, each with its fraction of the measured peak.
 
+`--only fozutar` (not part of the default run either) does the same for the Fozutar design (attention in chunks with a
+soft cap and a bias by distance, gated linear attention, dense and routed feed-forwards).
+
 This engine runs on one GPU: for --gpus > 1 it says so and exits with 2.
 
     python bench.py --kernel attention_prefill
@@ -654,6 +657,236 @@ def workload_venarax(a, pk):
             "data": "random-init weights drawn on the device, seeded uniform random token ids", "peaks": pk["source"], "sizes": out}
 
 
+def fozutar_config(raw, layers, chunk=1024):
+    """A Fozutar configuration with the layer sizes of the Qwen2 shape `raw`: the same width, heads, key heads, head size
+    and vocabulary; every third layer an attention layer (chunks of `chunk` positions, a bias table of 32 rows that
+    reaches 4,096), the others gated linear attention with half as many heads of twice the value size (keys half the width,
+    values the whole width, a decay projection of rank 16); the feed-forwards dense (the shape's own size) and routed (eight
+    experts of half that size, two a token: the same multiply-adds a token) in turn; no loop."""
+    d, i, v, hq, hkv, hd = sizes(raw)
+    att = {"type": "attention", "mixer": {"heads": hq, "kv_heads": hkv, "dim": hd, "vdim": hd, "scale": hd ** -0.5, "softcap": 50.0,
+                                          "bias_rows": 32, "bias_max": 4096, "mask": {"size": chunk}}}
+    gla = {"type": "gla", "mixer": {"heads": max(1, hq // 2), "dim": hd, "vdim": 2 * hd, "tau": 16.0, "decay_rank": 16}}
+    dense = {"kind": "dense", "ff": i}
+    moe = {"kind": "moe", "expert": {"ff": i // 2 // 32 * 32}, "router": {"experts": 8, "top": 2}}
+    return {"architecture": "Fozutar", "vocab": v, "width": d, "max_positions": 8192, "norm": {"eps": 1e-6}, "embedding": {"scale": 1.0},
+            "layers": [{**(att if n % 3 == 2 else gla), "mlp": moe if n % 2 else dense} for n in range(layers)]}
+
+
+def time_fozutar_kernels(torch, ops, raw, pk):
+    """The Fozutar design's kernels alone, each beside the like kernel of the dense decoder at equal sizes where there is
+    one (inputs larger than the L2; a CUDA graph of a few launches between events)."""
+    d, inter, _, hq, hkv, hd = sizes(raw)
+    dev, bf = "cuda:0", torch.bfloat16
+    g = torch.Generator(device=dev).manual_seed(0)
+    rnd = lambda *shape, dt=torch.float32, scale=1.0: (torch.randn(*shape, device=dev, generator=g) * scale).to(dt)
+
+    def us(fn, reps=5):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for _ in range(reps):
+                fn()
+        graph.replay()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        graph.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / reps * 1000
+
+    out = {}
+
+    def entry(name, t_new, t_like=None, nbytes=None, flops=None, like_bytes=None, like_flops=None, like="(no like kernel)"):
+        e = {"us": round(t_new, 1), "like": like}
+        if t_like is not None:
+            e["like_us"] = round(t_like, 1)
+        if nbytes:
+            e["hbm_frac"] = round(nbytes / t_new / 1e3 / pk["hbm_gbs"], 3)
+            if t_like is not None:
+                e["like_hbm_frac"] = round((like_bytes or nbytes) / t_like / 1e3 / pk["hbm_gbs"], 3)
+        if flops:
+            e["tensor_frac"] = round(flops / t_new / 1e6 / pk["bf16_tflops"], 4)
+            if t_like is not None:
+                e["like_tensor_frac"] = round((like_flops or flops) / t_like / 1e6 / pk["bf16_tflops"], 4)
+        out[name] = e
+
+    # the norm that adds a layer's two halves: 32,768 rows
+    rows = 32768
+    res, da, db = rnd(rows, d), rnd(rows, d), rnd(rows, d)
+    w = rnd(d)
+    o1 = torch.empty(rows, d, dtype=bf, device=dev)
+    t_new = us(lambda: ops.add_streams_rmsnorm(res, da, db, None, None, w, o1, 1e-6))
+    t_like = us(lambda: ops.add_rmsnorm(res, da, w, o1, 1e-6))
+    entry("add_streams_rmsnorm", t_new, t_like, rows * d * (4 + 4 + 4 + 4 + 2), like_bytes=rows * d * (4 + 4 + 4 + 2), like="add_rmsnorm (one delta)")
+    del res, da, db, o1
+    # gating: 16,384 rows of the feed-forward's width
+    rows = 16384
+    gu16 = rnd(rows, 2 * inter, dt=bf)
+    h = torch.empty(rows, inter, dtype=bf, device=dev)
+    t_new = us(lambda: ops.gated_act_mul(gu16, h, "gelu_tanh"))
+    t_like = us(lambda: ops.silu_mul(gu16, h))
+    entry("gated_act_mul_gelu", t_new, t_like, rows * inter * 6, like="silu_mul")
+    del gu16, h
+    # between the input product and the attention: 16,384 rows
+    page = PAGE
+    pos = (torch.arange(rows, dtype=torch.int32, device=dev) % 4096).contiguous()
+    slot = (torch.arange(rows, dtype=torch.int32, device=dev) // 4096).contiguous()
+    pages = rows // page
+    table = torch.arange(pages, dtype=torch.int32, device=dev).view(4, -1).contiguous()
+    proj = rnd(rows, (hq + hkv) * hd)
+    kp, vp = torch.zeros(pages, hkv, page, hd, dtype=bf, device=dev), torch.zeros(pages, hkv, page, hd, dtype=bf, device=dev)
+    qo = torch.empty(rows, hq * hd, device=dev)
+    t_new = us(lambda: ops.head_norm_store(proj, 1e-6, pos, slot, table, qo, kp, vp, hq, hkv, hd, hd, None))
+    proj16, qo16 = rnd(rows, (hq + 2 * hkv) * hd, dt=bf), torch.empty(rows, hq * hd, dtype=bf, device=dev)
+    ang = torch.zeros(4096, hd // 2, 2, device=dev)
+    t_like = us(lambda: ops.rope_kv_store(proj16, None, pos, slot, table, ang, hd, False, qo16, kp, vp, hq, hkv, hd))
+    entry("head_norm_store", t_new, t_like, rows * ((hq + hkv) * hd * 4 + hq * hd * 4 + 2 * hkv * hd * 2),
+          like_bytes=rows * ((hq + 2 * hkv) * hd * 2 + hq * hd * 2 + 2 * hkv * hd * 2), like="rope_kv_store (bfloat16 in and out)")
+    del proj, proj16, qo, qo16, kp, vp
+    # attention with cap, bias and chunks of 1,024: 64 decoding rows at 4,096 tokens, and one prompt of 4,096 tokens
+    from machserve_b200.parts.chunked_attention import bias_by_distance
+
+    chunk, ctx, b = 1024, 4096, 64
+    pages = b * ctx // page
+    table = torch.arange(pages, dtype=torch.int32, device=dev).view(b, -1).contiguous()
+    kp, vp = rnd(pages, hkv, page, hd, dt=bf), rnd(pages, hkv, page, hd, dt=bf)
+    score = ops.ScoreExtras(50.0, bias_by_distance(torch.randn(32, hq), 4096, chunk).to(dev), chunk)
+    q = rnd(b, hq * hd)
+    o = torch.empty(b, hq * hd, dtype=bf, device=dev)
+    posd = torch.full((b,), ctx - 1, dtype=torch.int32, device=dev)
+    slotd = torch.arange(b, dtype=torch.int32, device=dev)
+    items = b * hkv * (-(-(hq // hkv) // 16))
+    splits = max(1, min(6 * 148 // items, -(-(chunk + 63) // 64), 32))
+    scratch = torch.empty(max(1, ops.attention_wide_mma_scratch_words(items, hd, splits)), device=dev)
+    t_new = us(lambda: ops.attention_wide_mma(q, kp, vp, o, None, posd, slotd, table, None, None, b, True, hq, hkv, hd, hd, None, 0.1, splits,
+                                              scratch, score=score))
+    from types import SimpleNamespace
+
+    from machserve_b200.parts.attention import decode_launch
+
+    q16 = q.to(bf)
+    sp, stg, wr, kpw, parts = decode_launch(SimpleNamespace(sm_count=ops.sm_count()), hd, ops.attention_decode_cluster_max_stages(hd), {},
+                                            b * hkv, -(-chunk // 64))
+    t_like = us(lambda: ops.attention_decode_cluster(q16, kp, vp, o, posd, slotd, table, hq, hkv, hd, chunk, 0.1, sp, stg, warps=wr,
+                                                     keys_per_warp=kpw, parts=1))
+    entry("chunked_attention_decode", t_new, t_like, b * chunk * hkv * 2 * hd * 2, like="attention_decode_cluster under a window of 1,024")
+    n = ctx
+    posp = torch.arange(n, dtype=torch.int32, device=dev)
+    slotp = torch.zeros(n, dtype=torch.int32, device=dev)
+    qp, op = rnd(n, hq * hd), torch.empty(n, hq * hd, dtype=bf, device=dev)
+    tile = ops.attention_wide_mma_tile_rows(hd)
+    u0 = torch.arange(0, n, tile, dtype=torch.int32, device=dev)
+    un = torch.full_like(u0, tile)
+    t_new = us(lambda: ops.attention_wide_mma(qp, kp, vp, op, None, posp, slotp, table, u0, un, u0.numel(), False, hq, hkv, hd, hd, None, 0.1,
+                                              score=score), reps=2)
+    pairs = sum(p % chunk + 1 for p in range(n))
+    flops = 4 * pairs * hq * hd
+    t_like, like_flops = None, None
+    if ops.attention_prefill_tc_supports(hd, page):
+        qp16 = qp.to(bf)
+        t0 = torch.arange(0, n, 128, dtype=torch.int32, device=dev)
+        tn = torch.full_like(t0, 128)
+        tiles = t0.numel()
+        splits_p, alone, run_tiles = ops.attention_prefill_tc_plan(tiles, hq, hkv, hd, chunk + 128, tiles * 9)
+        words = ops.attention_prefill_tc_scratch_words(tiles, hq, hd, splits_p)
+        scr = torch.zeros(max(words, 1), dtype=torch.float32, device=dev) if words else None
+        counters = torch.zeros(tiles * hq, dtype=torch.int32, device=dev) if words else None
+        t_like = us(lambda: ops.attention_prefill_tc(qp16, kp, vp, op, t0, tn, tiles, posp, slotp, table, hq, hkv, hd, chunk, 0.1, splits_p,
+                                                     scr, counters, alone=alone, run_tiles=run_tiles), reps=2)
+        like_flops = 4 * sum(min(p + 1, chunk) for p in range(n)) * hq * hd
+    entry("chunked_attention_prefill", t_new, t_like, flops=flops, like_flops=like_flops,
+          like="attention_prefill_tc (tcgen05) under a window of 1,024" if t_like else "(no like kernel)")
+    del kp, vp, q, o, qp, op
+    # the recurrence: 64 sequences of one token (the states alone are past the L2 at the larger shapes), and one of 4,096
+    heads, dk, dv = max(1, hq // 2), hd, 2 * hd
+    kw, vw = heads * dk, heads * dv
+    state = torch.zeros(b, heads, dk, dv, device=dev)
+    proj = rnd(n, 2 * kw + 2 * vw + 16, scale=0.1)
+    dec = -torch.rand(n, kw, device=dev, generator=g) * 0.1
+    og = torch.empty(n, vw, device=dev)
+    cu1 = torch.arange(b + 1, dtype=torch.int32, device=dev)
+    t_new = us(lambda: ops.gla_scan(proj[:b], 0, kw, 2 * kw, dec[:b], 0.1, state, cu1, slotd, slotd, og[:b], b, heads, dk, dv))
+    entry("gla_scan_decode", t_new, nbytes=2 * b * heads * dk * dv * 4)
+    cup = torch.tensor([0, n], dtype=torch.int32, device=dev)
+    zero = torch.zeros(n, dtype=torch.int32, device=dev)
+    t_new = us(lambda: ops.gla_scan(proj, 0, kw, 2 * kw, dec, 0.1, state, cup, zero[:1], zero, og, 1, heads, dk, dv), reps=2)
+    entry("gla_scan_prefill", t_new, flops=n * heads * dk * dv * 4)  # (CUDA-core multiply-adds: the scan is sequential)
+    w2 = rnd(kw, 16, dt=bf)
+    y = torch.empty(n, vw, dtype=bf, device=dev)
+    normw = rnd(dv)
+    t_new = us(lambda: (ops.gla_decay(proj[:, 2 * kw + 2 * vw:], w2, None, 16.0, dec), ops.gla_output(og, proj[:, 2 * kw + vw: 2 * kw + 2 * vw], normw, 1e-6, y, heads, dv)))
+    entry("gla_decay_and_output", t_new, nbytes=n * (16 * 4 + kw * 4 + vw * 4 + vw * 4 + vw * 2))
+    del state, proj, dec, og, y
+    # the routed feed-forward: eight experts of half the dense size, two a token; 8 decoding rows and 4,096 rows of a prompt
+    experts, top, ff = 8, 2, inter // 2 // 32 * 32
+    wg, wu, wd = rnd(experts, ff, d, dt=bf, scale=0.02), rnd(experts, ff, d, dt=bf, scale=0.02), rnd(experts, d, ff, dt=bf, scale=0.02)
+    for t, name in ((8, "routed_experts_decode"), (4096, "routed_experts_prefill")):
+        x = rnd(t, d, dt=bf)
+        logits = rnd(t, experts)
+        ids, weights = torch.empty(t, top, dtype=torch.int32, device=dev), torch.empty(t, top, device=dev)
+        ops.moe_route(logits, top, ids, weights)
+        hbuf = torch.empty(t * top, ff, dtype=bf, device=dev)
+        yb = torch.empty(t, d, device=dev)
+        slots = torch.zeros(t, dtype=torch.int32, device=dev)
+        w_dense = rnd(2 * inter, d, dt=bf, scale=0.02)
+        w_down = rnd(d, inter, dt=bf, scale=0.02)
+        gu = torch.empty(t, 2 * inter, dtype=bf, device=dev)
+        hd_ = torch.empty(t, inter, dtype=bf, device=dev)
+        od = torch.empty(t, d, dtype=bf, device=dev)
+        if t <= 16:
+            t_new = us(lambda: (ops.moe_route(logits, top, ids, weights), ops.moe_gate_up_pairs(x, wg, wu, ids, slots, hbuf, "silu"),
+                                ops.moe_down_pairs(hbuf, wd, ids, weights, slots, yb)))
+            t_like = us(lambda: (ops.gemm_small_m_silu_mul(x, w_dense[:inter], w_dense[inter:], hd_), ops.linear(hd_, w_down, None, od)))
+            touched = min(experts, t * top)
+            entry(name, t_new, t_like, nbytes=touched * 3 * ff * d * 2, like_bytes=3 * inter * d * 2,
+                  like="the dense gated feed-forward of the same multiply-adds a token (few-row products)")
+        else:
+            scratch = torch.empty(ops.moe_grouped_scratch_ints(t * top, experts), dtype=torch.int32, device=dev)
+            z = torch.empty(t * top, d, device=dev)
+            t_new = us(lambda: (ops.moe_route(logits, top, ids, weights), ops.moe_grouped(x, wg, wu, wd, ids, weights, slots, scratch, hbuf, z, yb, "silu")), reps=2)
+            t_like = us(lambda: (ops.linear(x, w_dense, None, gu), ops.silu_mul(gu, hd_), ops.linear(hd_, w_down, None, od)), reps=2)
+            entry(name, t_new, t_like, flops=6 * t * top * ff * d, like_flops=6 * t * inter * d,
+                  like="the dense gated feed-forward of the same multiply-adds a token (library products)")
+    return out
+
+
+def workload_fozutar(a, pk):
+    """The Fozutar design at the layer sizes of the Qwen2.5 shapes, beside the dense decoder at the same sizes: decode
+    at the headline batch and context, one prompt of `--prefill` tokens, and the new kernels alone."""
+    import torch
+
+    from machserve_b200 import ops
+
+    out = {}
+    shapes = sorted(SHAPES) if a.fozutar_shapes == "all" else [x.strip() for x in a.fozutar_shapes.split(",") if x.strip()]
+    for shape in shapes:
+        raw = SHAPES[shape]
+        layers = min(raw["num_hidden_layers"], a.layers or 12)  # (layers of like sizes: twelve tell what all tell)
+        res = {"layers": layers}
+        steps = max(10, a.steps // 2)
+        for which in ("fozutar", "dense"):
+            kw = dict(config=fozutar_config(raw, layers), vocab=raw["vocab_size"]) if which == "fozutar" else {}
+            b = DecodeBench(a, raw, layers, "bf16", a.batch, a.context + 4 * (steps + a.warmup) + a.batch + 64, **kw)
+            times, launches = b.time_decode(a.batch, a.context, steps, a.warmup, blocks=3, sampled=False)
+            pms = b.time_prefill(a.prefill, 2, reps=3)
+            res[which] = {"decode_ms_per_step": round(times[len(times) // 2], 4), "decode_tokens_per_s": round(a.batch * 1000.0 / times[len(times) // 2], 1),
+                          "launches_per_step": launches // steps, "prefill_ms": round(pms, 3), "prefill_tokens_per_s": round(a.prefill * 1000.0 / pms, 1)}
+            b.runner.check_device_status()
+            b.release_all()
+            del b
+            free_device_memory()
+        if not a.no_points:
+            res["kernels"] = time_fozutar_kernels(torch, ops, raw, pk)
+        free_device_memory()
+        out[shape] = res
+    return {"batch": a.batch, "context": a.context, "prefill_tokens": a.prefill, "dtype": "bf16",
+            "data": "random-init weights drawn on the device, seeded uniform random token ids", "peaks": pk["source"], "sizes": out}
+
+
 def workload_serving(a, pk):
     """Qwen2.5-1.5B sizes: 64 requests, prompts of 128 to 2,048 tokens (seeded), 256 new tokens each, through `Engine`
     with its default budget of prompt tokens per step.  All requests arrive at time zero.  Three loads of other prompt
@@ -836,9 +1069,11 @@ def main() -> int:
     ap.add_argument("--dtype", default="bf16", choices=["bf16", "bfloat16", "f32", "fp32", "float32"])
     ap.add_argument("--only", default="headline,fp32,serving_1p5b,mixed_7b",
                     help="which parts to run: headline, fp32, serving_1p5b, mixed_7b (comma separated); venarax, which is not "
-                         "among the defaults, times the Venarax design beside the dense decoder at equal layer sizes")
+                         "among the defaults, times the Venarax design beside the dense decoder at equal layer sizes; fozutar, "
+                         "likewise not among the defaults, does the same for the Fozutar design")
     ap.add_argument("--no-points", action="store_true", help="skip the further batch sizes and the prefill (venarax: the kernels alone)")
     ap.add_argument("--venarax-shapes", default="all", help="the shapes of the venarax workload (comma separated), or all")
+    ap.add_argument("--fozutar-shapes", default="all", help="the shapes of the fozutar workload (comma separated), or all")
     ap.add_argument("--profile", default=None, choices=["decode", "prefill", "mixed"],
                     help="which timed region is bracketed by cudaProfilerStart/Stop (for ncu --profile-from-start off)")
     ap.add_argument("--kernel", default=None, choices=["attention_prefill", "gemm"],
@@ -954,6 +1189,8 @@ def main() -> int:
         line["mixed_7b"] = workload_mixed(a, pk)
     if "venarax" in only:
         line["venarax"] = workload_venarax(a, pk)
+    if "fozutar" in only:
+        line["fozutar"] = workload_fozutar(a, pk)
     print(json.dumps(line))
     return 0
 

@@ -87,6 +87,7 @@ class _Signatures:
     ms_moe_route = [P, I, I, P, P, I, P]
     ms_moe_gate_up_pairs = [P, P, P, P, P, P, I, I, I, I, I, I, I, P]
     ms_moe_down_pairs = [P, P, P, P, P, P, I, I, I, I, I, I, P]
+    ms_moe_grouped = [P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, P]
     ms_attention_wide = [P, P, P, P, I, P, P, P, P, I, I, I, I, I, I, I, I, I, I, F, I, P]
     ms_attention_wide_mma = [P, P, P, P, P, P, P, P, I, I, P, P, I, I, I, I, I, I, I, I, I, F, I, P, P]
     ms_rope_kv_store = [P, I, I, P, P, P, P, I, I, P, I, I, P, P, P, I, I, I, I, I, I, P]
@@ -1306,6 +1307,42 @@ def moe_down_pairs(h, w_down, ids, weights, slot_of_token, y):
         n = min(65535, t - t0)
         _check(lib().ms_moe_down_pairs(_ptr(h[t0 * top:]), _ptr(w_down), _ptr(ids[t0:]), _ptr(weights[t0:]), _ptr(slot_of_token[t0:]),
                                        _ptr(y[t0:]), _code(h), n, top, d, ff, experts, _stream()), "moe_down_pairs")
+    return y
+
+
+def moe_grouped_supports(d: int, ff: int, experts: int) -> bool:
+    """Whether the sorted, tiled form of the routed feed-forward covers the sizes (both widths multiples of 32)."""
+    return bool(lib().ms_moe_grouped_supports(int(d), int(ff), int(experts)))
+
+
+def moe_grouped_scratch_ints(pairs: int, experts: int) -> int:
+    fn = lib().ms_moe_grouped_scratch_ints
+    fn.restype = c_longlong
+    fn.argtypes = [c_int, c_int]
+    return int(fn(int(pairs), int(experts)))
+
+
+def moe_grouped(x, w_gate, w_up, w_down, ids, weights, slot_of_token, scratch, h, z, y, activation: str):
+    """The routed feed-forward for many rows, bfloat16, on the tensor cores: the (token, expert) pairs sorted by expert on
+    the device, every expert's rows through its matrices in tiles, the pairs' results summed per token with the router's
+    weights (j ascending).  x [T, d]; w_gate, w_up [E, ff, d]; w_down [E, d, ff]; ids int32, weights float32 [T, top];
+    scratch int32 (`moe_grouped_scratch_ints`), h bfloat16 [T*top, ff], z float32 [T*top, d]; y float32 [T, d]."""
+    t, d = x.shape
+    experts, ff, _ = w_gate.shape
+    top = ids.shape[1]
+    bf = torch.bfloat16
+    _need(x.dtype == bf and w_gate.dtype == bf and w_up.dtype == bf and w_down.dtype == bf and h.dtype == bf and x.is_contiguous()
+          and w_gate.is_contiguous() and w_up.is_contiguous() and w_down.is_contiguous() and h.is_contiguous(), "moe_grouped: bad operands")
+    _need(tuple(w_up.shape) == (experts, ff, d) and tuple(w_down.shape) == (experts, d, ff) and w_gate.shape[2] == d
+          and tuple(h.shape) == (t * top, ff) and tuple(z.shape) == (t * top, d) and tuple(y.shape) == (t, d)
+          and z.dtype == torch.float32 and y.dtype == torch.float32 and z.is_contiguous() and y.is_contiguous(), "moe_grouped: bad shapes")
+    _need(ids.dtype == torch.int32 and ids.is_contiguous() and weights.dtype == torch.float32 and weights.is_contiguous()
+          and tuple(weights.shape) == (t, top) and scratch.dtype == torch.int32
+          and scratch.numel() >= moe_grouped_scratch_ints(t * top, experts), "moe_grouped: bad lists")
+    _check(lib().ms_moe_grouped(_ptr(x), _ptr(w_gate), _ptr(w_up), _ptr(w_down), _ptr(ids), _ptr(weights), _ptr(slot_of_token), _ptr(scratch),
+                                _ptr(h), _ptr(z), _ptr(y), t, top, d, ff, experts, ACTIVATIONS[activation], _stream()), "moe_grouped")
+    global _launches
+    _launches += 3  # the sort, two products and the sum are four launches
     return y
 
 

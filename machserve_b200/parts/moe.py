@@ -20,6 +20,7 @@ class RoutedExperts(FeedForward):
     """
 
     graph_safe = True
+    GROUPED_FROM_ROWS = 17  # fewer rows stream the chosen experts' rows pair by pair (decoding)
 
     def __init__(self, spec):
         super().__init__(spec)
@@ -50,6 +51,7 @@ class RoutedExperts(FeedForward):
         self.b_router = vector_f32(tensors[p + "router.b"]) if self.router_bias else None
         stack = lambda name: matrix(torch.stack([tensors[f"{p}e{e}.{name}"] for e in range(self.experts)], dim=0), rt)
         self.w_gate, self.w_up, self.w_down = stack("gate"), stack("up"), stack("down")
+        self.grouped = rt.dtype == torch.bfloat16 and ops.moe_grouped_supports(self.hidden, self.inter, self.experts)
 
     def forward(self, ctx, x):
         rt, t = self.rt, x.shape[0]
@@ -60,6 +62,12 @@ class RoutedExperts(FeedForward):
         weights = ws.get("moe.weights", (t, self.top), torch.float32)
         ops.moe_route(logits, self.top, ids, weights)
         h = ws.get("moe.h", (t * self.top, self.inter), rt.dtype)
-        ops.moe_gate_up_pairs(x, self.w_gate, self.w_up, ids, ctx.slot_of_token, h, self.activation)
         delta = ws.get("ffn.delta_f32", (t, self.hidden), torch.float32)
+        if self.grouped and t >= self.GROUPED_FROM_ROWS and t * self.top // 64 + self.experts <= 65535:
+            # many rows: sorted by expert on the device, every expert's rows in tiles on the tensor cores
+            scratch = ws.get("moe.sorted", (ops.moe_grouped_scratch_ints(t * self.top, self.experts),), torch.int32)
+            z = ws.get("moe.z", (t * self.top, self.hidden), torch.float32)
+            return ops.moe_grouped(x, self.w_gate, self.w_up, self.w_down, ids, weights, ctx.slot_of_token, scratch, h, z, delta,
+                                   self.activation)
+        ops.moe_gate_up_pairs(x, self.w_gate, self.w_up, ids, ctx.slot_of_token, h, self.activation)
         return ops.moe_down_pairs(h, self.w_down, ids, weights, ctx.slot_of_token, delta)

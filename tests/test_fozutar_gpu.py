@@ -417,6 +417,45 @@ def test_router_and_experts(experts, top, d, ff, dtype):
     assert_close(y.cpu().numpy(), want, 2e-5 if dtype == "float32" else 2e-2, f"{top} of {experts} experts")
 
 
+@pytest.mark.parametrize("experts,top,d,ff,t", [(5, 2, 64, 32, 70), (3, 3, 96, 64, 23), (9, 1, 32, 160, 300), (12, 4, 128, 96, 777)])
+def test_experts_in_sorted_tiles(experts, top, d, ff, t):
+    """The form for many rows: pairs sorted by expert on the device, tiles of 64 rows on the tensor cores.  Experts that
+    nobody chose, experts with more rows than a tile, rows of no request."""
+    torch = _torch()
+    from machserve_b200 import ops
+
+    rng = np.random.default_rng(experts * 100 + t)
+    bf = torch.bfloat16
+    h = _bf16(rng.normal(size=(t, d)))
+    w = {}
+    for e in range(experts):
+        w[f"e{e}.gate"], w[f"e{e}.up"], w[f"e{e}.down"] = (_bf16(0.3 * rng.normal(size=s)) for s in ((ff, d), (ff, d), (d, ff)))
+    logits = rng.normal(size=(t, experts))
+    logits[:, experts - 1] -= 50.0 if experts > top else 0.0  # an expert that is never chosen
+    logits[: t // 2, 0] += 3.0  # and one that half of the rows choose
+    ids = torch.empty((t, top), dtype=torch.int32, device="cuda")
+    weights = torch.empty((t, top), dtype=torch.float32, device="cuda")
+    ops.moe_route(_dev(logits.astype(np.float32)), top, ids, weights)
+    slots = np.zeros(t, dtype=np.int32)
+    slots[[4, t - 1]] = -1
+    stack = lambda name: _dev(np.stack([w[f"e{e}.{name}"] for e in range(experts)]).astype(np.float32), bf)
+    assert ops.moe_grouped_supports(d, ff, experts)
+    scratch = torch.empty(ops.moe_grouped_scratch_ints(t * top, experts), dtype=torch.int32, device="cuda")
+    hid = torch.empty((t * top, ff), dtype=bf, device="cuda")
+    z = torch.empty((t * top, d), dtype=torch.float32, device="cuda")
+    y = torch.empty((t, d), dtype=torch.float32, device="cuda")
+    ops.moe_grouped(_dev(h.astype(np.float32), bf), stack("gate"), stack("up"), stack("down"), ids, weights, _dev(slots), scratch, hid, z, y, "silu")
+    got_ids, got_w = ids.cpu().numpy(), weights.cpu().numpy().astype(np.float64)
+    want = np.zeros((t, d))
+    for r in range(t):
+        if slots[r] < 0:
+            continue
+        for e, a in zip(got_ids[r], got_w[r]):
+            hidden = _bf16(plain.silu(w[f"e{e}.gate"] @ h[r]) * (w[f"e{e}.up"] @ h[r]))  # (the engine hands it on in bfloat16)
+            want[r] += a * (hidden @ w[f"e{e}.down"].T)
+    assert_close(y.cpu().numpy(), want, 2e-3, f"{top} of {experts} experts over {t} rows")
+
+
 # ----------------------------------------------------------------------------------- the model, cut every way
 
 
