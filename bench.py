@@ -842,8 +842,12 @@ def time_fozutar_kernels(torch, ops, raw, pk):
                                 ops.moe_down_pairs(hbuf, wd, ids, weights, slots, yb)))
             t_like = us(lambda: (ops.gemm_small_m_silu_mul(x, w_dense[:inter], w_dense[inter:], hd_), ops.linear(hd_, w_down, None, od)))
             touched = min(experts, t * top)
+            scratch = torch.empty(ops.moe_grouped_scratch_ints(t * top, experts), dtype=torch.int32, device=dev)
+            z = torch.empty(t * top, d, device=dev)
+            t_tiles = us(lambda: (ops.moe_route(logits, top, ids, weights), ops.moe_grouped(x, wg, wu, wd, ids, weights, slots, scratch, hbuf, z, yb, "silu")))
             entry(name, t_new, t_like, nbytes=touched * 3 * ff * d * 2, like_bytes=3 * inter * d * 2,
                   like="the dense gated feed-forward of the same multiply-adds a token (few-row products)")
+            out[name]["sorted_tiles_us"] = round(t_tiles, 1)  # (the form for many rows, at these few)
         else:
             scratch = torch.empty(ops.moe_grouped_scratch_ints(t * top, experts), dtype=torch.int32, device=dev)
             z = torch.empty(t * top, d, device=dev)

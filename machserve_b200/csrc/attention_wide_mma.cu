@@ -22,6 +22,11 @@
 // NW: warps of a block, 4, or 8 for decoding rows where the values are 256 or more columns wide (half the accumulators
 // a warp, twice the warps an SM).  DVW: value columns a warp owns (the block covers NW * DVW >= dv).
 // MT: tiles of 16 query rows a block attends.  A warp takes 64 / NW keys of a tile in the score phase.
+__device__ __forceinline__ float awm_tanh(float x) {
+  float y;
+  asm("tanh.approx.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+  return y;
+}
 __device__ __forceinline__ void awm_ldmatrix_x2(unsigned& r0, unsigned& r1, const void* p) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2];\n" : "=r"(r0), "=r"(r1) : "r"(ms_smem_addr(p)));
 }
@@ -93,6 +98,7 @@ attention_wide_mma_kernel(const float* __restrict__ q, const __nv_bfloat16* __re
       if (ex.chunk > 0) lo[t][i] = max(lo[t][i], p / ex.chunk * ex.chunk);
     }
 
+  const float inv_cap = ex.softcap > 0.f ? 1.f / ex.softcap : 0.f;
   float o[MT][DVW / 8][4];
   float m[MT][2], l[MT][2];
 #pragma unroll
@@ -198,7 +204,7 @@ attention_wide_mma_kernel(const float* __restrict__ q, const __nv_bfloat16* __re
             sc = s[t][n][i] * scale_log2;
             if (ex.softcap > 0.f || ex.dist_bias) {  // back to natural units: the cap and the bias are not scaled
               sc *= 0.6931471805599453f;
-              if (ex.softcap > 0.f) sc = ex.softcap * tanhf(sc / ex.softcap);
+              if (ex.softcap > 0.f) sc = ex.softcap * awm_tanh(sc * inv_cap);  // (P is rounded to bfloat16 right after)
               if (ex.dist_bias) {
                 const int head = HEADS ? head0 + t * AWM_ROWS + (lane >> 2) + 8 * r : head0;
                 sc += ex.dist_bias[(size_t)head * ex.dist_len + min(hi[t][r] - key, ex.dist_len - 1)];

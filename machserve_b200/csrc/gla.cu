@@ -10,15 +10,16 @@
 // gla_decay:   g[t, n] = logsigmoid(sum_r W2[n, r] * u[t, r] + b2[n]) / tau; one thread an output.
 // gla_scan:    a block owns 32 value columns of one head of one sequence and goes through the sequence's rows of the step in
 //              order, from the state the step found to the state it leaves.  Thread (c, g) holds KPT consecutive key rows of
-//              column c in registers; q, k and exp(g) of TB tokens at a time are staged in shared memory; the partial
-//              outputs of the eight row groups are summed in group order.  The arithmetic of a token depends on the
-//              tokens before it alone, not on how the sequence was cut into steps or on what else is in the batch.
+//              column c in registers; q, k and exp(g) of TB tokens at a time are staged in shared memory, the next batch on
+//              its way while this one is worked on; the partial outputs of the eight row groups are summed in group order.
+//              The arithmetic of a token depends on the tokens before it alone, not on how the sequence was cut into steps
+//              or on what else is in the batch.
 // gla_output:  the norm over a head's dv outputs, its weight, and the gate; one warp a (token, head).
 #include "launch.cuh"
 
 #define GLA_COLS 32
 #define GLA_GROUPS 8
-#define GLA_TB 8
+#define GLA_TB 16
 
 template <typename TW>
 __global__ void gla_decay_kernel(const float* __restrict__ u, int ldu, const TW* __restrict__ w2, const float* __restrict__ b2, int rank,
@@ -58,15 +59,22 @@ MS_API int ms_gla_decay(const float* u, int ldu, const void* w2, int w_dtype, co
 
 // q, k, v: float32 rows of one product, row stride ld, at column offsets q_off, k_off, v_off; within each, head h begins at
 // h*dk (q, k) or h*dv (v).  g: float32 [T, heads*dk].  state: float32 [slots, heads, dk, dv].  o: float32 [T, heads*dv].
+// The rows of GLA_TB tokens at a time come into shared memory by asynchronous copies, one batch ahead of the one that is
+// worked on (two places); a pass over a landed batch turns g into exp(g) and scales q, once for all columns.
+__device__ __forceinline__ void gla_cp_async4(float* smem, const float* gmem) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"((unsigned)__cvta_generic_to_shared(smem)), "l"(gmem));
+}
+
 template <int KPT>
 __global__ void __launch_bounds__(GLA_COLS * GLA_GROUPS)
 gla_scan_kernel(const float* __restrict__ proj, int ld, int q_off, int k_off, int v_off, const float* __restrict__ g, float q_scale,
                 float* __restrict__ state, const int* __restrict__ cu_tokens, const int* __restrict__ state_slots,
                 const int* __restrict__ slot_of_token, float* __restrict__ o, int heads, int dk, int dv) {
-  constexpr int KP = KPT * GLA_GROUPS;  // key rows, padded
-  __shared__ __align__(16) float q_s[GLA_TB][KP], k_s[GLA_TB][KP], a_s[GLA_TB][KP];
-  __shared__ float v_s[GLA_TB][GLA_COLS];
-  __shared__ float part[GLA_TB][GLA_GROUPS][GLA_COLS];
+  constexpr int KP = KPT * GLA_GROUPS;             // key rows, padded
+  constexpr int ROW = 3 * KP + GLA_COLS;           // floats of one token in a stage: q | k | a | v
+  extern __shared__ __align__(16) float gla_smem[];
+  float* stage0 = gla_smem;                        // [2][GLA_TB][ROW]
+  float* part = gla_smem + 2 * GLA_TB * ROW;       // [GLA_TB][GLA_GROUPS][GLA_COLS]
   ms_pdl_trigger();
   ms_pdl_wait();
   const int seq = blockIdx.z, h = blockIdx.y, c0 = blockIdx.x * GLA_COLS;
@@ -76,6 +84,34 @@ gla_scan_kernel(const float* __restrict__ proj, int ld, int q_off, int k_off, in
   const int c = threadIdx.x % GLA_COLS, grp = threadIdx.x / GLA_COLS;
   const int col = c0 + c;
   const bool live = col < dv;
+  // padding of the key rows: q = k = 0 and a = 1 for good, in both stages
+  for (int e = threadIdx.x; e < 2 * GLA_TB * (KP - dk); e += blockDim.x) {
+    const int tb = e / (KP - dk), r = dk + e % (KP - dk);
+    float* t = stage0 + (size_t)tb * ROW;
+    t[r] = 0.f;
+    t[KP + r] = 0.f;
+    t[2 * KP + r] = 1.f;
+  }
+  auto request = [&](int t0, int st) {
+    const int nt = min(GLA_TB, rows - t0);
+    float* base = stage0 + (size_t)st * GLA_TB * ROW;
+    for (int e = threadIdx.x; e < nt * dk; e += blockDim.x) {
+      const int tb = e / dk, r = e - tb * dk;
+      const size_t t = (size_t)(row0 + t0 + tb);
+      float* dst = base + (size_t)tb * ROW;
+      gla_cp_async4(dst + r, proj + t * ld + q_off + h * dk + r);
+      gla_cp_async4(dst + KP + r, proj + t * ld + k_off + h * dk + r);
+      gla_cp_async4(dst + 2 * KP + r, g + t * ((size_t)heads * dk) + h * dk + r);
+    }
+    for (int e = threadIdx.x; e < nt * GLA_COLS; e += blockDim.x) {
+      const int tb = e / GLA_COLS, cc = e - tb * GLA_COLS;
+      float* dst = base + (size_t)tb * ROW + 3 * KP + cc;
+      if (c0 + cc < dv) gla_cp_async4(dst, proj + (size_t)(row0 + t0 + tb) * ld + v_off + h * dv + c0 + cc);
+      else *dst = 0.f;
+    }
+  };
+  request(0, 0);
+  asm volatile("cp.async.commit_group;\n" ::);
   float* st = state + (((size_t)slot * heads + h) * dk) * dv;
   float s[KPT];
 #pragma unroll
@@ -83,42 +119,43 @@ gla_scan_kernel(const float* __restrict__ proj, int ld, int q_off, int k_off, in
     const int r = grp * KPT + i;
     s[i] = (live && r < dk) ? st[(size_t)r * dv + col] : 0.f;
   }
-  for (int t0 = 0; t0 < rows; t0 += GLA_TB) {
+  int stg = 0;
+  for (int t0 = 0; t0 < rows; t0 += GLA_TB, stg ^= 1) {
     const int nt = min(GLA_TB, rows - t0);
-    __syncthreads();  // the batch before has been read
-    for (int e = threadIdx.x; e < nt * KP; e += blockDim.x) {
-      const int tb = e / KP, r = e - tb * KP;
-      const size_t t = (size_t)(row0 + t0 + tb);
-      const bool in = r < dk;
-      q_s[tb][r] = in ? proj[t * ld + q_off + h * dk + r] * q_scale : 0.f;
-      k_s[tb][r] = in ? proj[t * ld + k_off + h * dk + r] : 0.f;
-      a_s[tb][r] = in ? expf(g[t * ((size_t)heads * dk) + h * dk + r]) : 1.f;
-    }
-    for (int e = threadIdx.x; e < nt * GLA_COLS; e += blockDim.x) {
-      const int tb = e / GLA_COLS, cc = e - tb * GLA_COLS;
-      v_s[tb][cc] = (c0 + cc < dv) ? proj[(size_t)(row0 + t0 + tb) * ld + v_off + h * dv + c0 + cc] : 0.f;
+    asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+    __syncthreads();  // the batch has landed for every thread; the batch before has been read and its outputs written
+    if (t0 + GLA_TB < rows) request(t0 + GLA_TB, stg ^ 1);
+    asm volatile("cp.async.commit_group;\n" ::);
+    float* base = stage0 + (size_t)stg * GLA_TB * ROW;
+    for (int e = threadIdx.x; e < nt * dk; e += blockDim.x) {  // (the padding rows keep q = k = 0 and a = 1)
+      const int tb = e / dk, r = e - tb * dk;
+      float* t = base + (size_t)tb * ROW;
+      t[r] *= q_scale;
+      t[2 * KP + r] = expf(t[2 * KP + r]);
     }
     __syncthreads();
+#pragma unroll 2
     for (int tb = 0; tb < nt; ++tb) {
-      const float v = v_s[tb][c];
-      float acc = 0.f;
+      const float* t = base + (size_t)tb * ROW;
+      const float v = t[3 * KP + c];
+      float acc0 = 0.f, acc1 = 0.f;  // two chains of sums (even and odd rows), added at the end: the order is fixed
 #pragma unroll
       for (int i = 0; i < KPT; i += 2) {  // (KPT is even)
-        const float2 a = *reinterpret_cast<const float2*>(&a_s[tb][grp * KPT + i]);
-        const float2 k = *reinterpret_cast<const float2*>(&k_s[tb][grp * KPT + i]);
-        const float2 q = *reinterpret_cast<const float2*>(&q_s[tb][grp * KPT + i]);
+        const float2 q = *reinterpret_cast<const float2*>(t + grp * KPT + i);
+        const float2 k = *reinterpret_cast<const float2*>(t + KP + grp * KPT + i);
+        const float2 a = *reinterpret_cast<const float2*>(t + 2 * KP + grp * KPT + i);
         s[i] = fmaf(a.x, s[i], k.x * v);
         s[i + 1] = fmaf(a.y, s[i + 1], k.y * v);
-        acc = fmaf(s[i], q.x, acc);
-        acc = fmaf(s[i + 1], q.y, acc);
+        acc0 = fmaf(s[i], q.x, acc0);
+        acc1 = fmaf(s[i + 1], q.y, acc1);
       }
-      part[tb][grp][c] = acc;
+      part[((size_t)tb * GLA_GROUPS + grp) * GLA_COLS + c] = acc0 + acc1;
     }
     __syncthreads();
     for (int tb = grp; tb < nt; tb += GLA_GROUPS) {
       float sum = 0.f;
 #pragma unroll
-      for (int gi = 0; gi < GLA_GROUPS; ++gi) sum += part[tb][gi][c];
+      for (int gi = 0; gi < GLA_GROUPS; ++gi) sum += part[((size_t)tb * GLA_GROUPS + gi) * GLA_COLS + c];
       if (live) o[(size_t)(row0 + t0 + tb) * ((size_t)heads * dv) + h * dv + col] = sum;
     }
   }
@@ -127,6 +164,23 @@ gla_scan_kernel(const float* __restrict__ proj, int ld, int q_off, int k_off, in
     const int r = grp * KPT + i;
     if (live && r < dk) st[(size_t)r * dv + col] = s[i];
   }
+}
+
+template <int KPT>
+static int gla_scan_launch(dim3 grid, dim3 block, cudaStream_t stream, const float* proj, int ld, int q_off, int k_off, int v_off,
+                           const float* g, float q_scale, float* state, const int* cu_tokens, const int* state_slots,
+                           const int* slot_of_token, float* o, int heads, int dk, int dv) {
+  constexpr int KP = KPT * GLA_GROUPS;
+  const size_t smem = (size_t)(2 * GLA_TB * (3 * KP + GLA_COLS) + GLA_TB * GLA_GROUPS * GLA_COLS) * sizeof(float);
+  static bool configured = false;
+  if (!configured && smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(gla_scan_kernel<KPT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    MS_REQUIRE(e == cudaSuccess, "gla_scan: cannot get %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
+    configured = true;
+  }
+  MS_LAUNCH_RESULT("gla_scan", ms_launch(gla_scan_kernel<KPT>, grid, block, smem, stream, 1, true, proj, ld, q_off, k_off, v_off, g, q_scale,
+                                         state, cu_tokens, state_slots, slot_of_token, o, heads, dk, dv));
+  return 0;
 }
 
 MS_API int ms_gla_scan(const float* proj, int ld, int q_off, int k_off, int v_off, const float* g, float q_scale, float* state,
@@ -138,19 +192,17 @@ MS_API int ms_gla_scan(const float* proj, int ld, int q_off, int k_off, int v_of
   MS_REQUIRE(seqs <= 65535 && heads <= 65535, "gla_scan: too many sequences or heads for one launch");
   const dim3 grid((dv + GLA_COLS - 1) / GLA_COLS, heads, seqs), block(GLA_COLS * GLA_GROUPS);
   const int kpt = (dk + GLA_GROUPS - 1) / GLA_GROUPS;
-#define MS_GLA_GO(K)                                                                                                                 \
-  MS_LAUNCH_RESULT("gla_scan", ms_launch(gla_scan_kernel<K>, grid, block, 0, stream, 1, true, proj, ld, q_off, k_off, v_off, g, q_scale, \
-                                         state, cu_tokens, state_slots, slot_of_token, o, heads, dk, dv))
+#define MS_GLA_GO(K) \
+  return gla_scan_launch<K>(grid, block, stream, proj, ld, q_off, k_off, v_off, g, q_scale, state, cu_tokens, state_slots, slot_of_token, o, heads, dk, dv)
   if (kpt <= 2) MS_GLA_GO(2);
-  else if (kpt <= 4) MS_GLA_GO(4);
-  else if (kpt <= 6) MS_GLA_GO(6);
-  else if (kpt <= 8) MS_GLA_GO(8);
-  else if (kpt <= 12) MS_GLA_GO(12);
-  else if (kpt <= 16) MS_GLA_GO(16);
-  else if (kpt <= 24) MS_GLA_GO(24);
-  else MS_GLA_GO(32);
+  if (kpt <= 4) MS_GLA_GO(4);
+  if (kpt <= 6) MS_GLA_GO(6);
+  if (kpt <= 8) MS_GLA_GO(8);
+  if (kpt <= 12) MS_GLA_GO(12);
+  if (kpt <= 16) MS_GLA_GO(16);
+  if (kpt <= 24) MS_GLA_GO(24);
+  MS_GLA_GO(32);
 #undef MS_GLA_GO
-  return 0;
 }
 
 template <typename TO>

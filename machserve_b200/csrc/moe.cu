@@ -74,12 +74,30 @@ __device__ __forceinline__ float moe_act(float g, int act) {
 
 #define MOE_WARPS 8
 
+// eight consecutive weights (16 bytes of bfloat16, 32 of float32) times eight floats of shared memory, added to s in order
+__device__ __forceinline__ float moe_dot8(const float* w, const float* x, float s) {
+  const float4 a = *reinterpret_cast<const float4*>(w), b = *reinterpret_cast<const float4*>(w + 4);
+  const float4 p = *reinterpret_cast<const float4*>(x), q = *reinterpret_cast<const float4*>(x + 4);
+  s = fmaf(a.x, p.x, s); s = fmaf(a.y, p.y, s); s = fmaf(a.z, p.z, s); s = fmaf(a.w, p.w, s);
+  s = fmaf(b.x, q.x, s); s = fmaf(b.y, q.y, s); s = fmaf(b.z, q.z, s); s = fmaf(b.w, q.w, s);
+  return s;
+}
+__device__ __forceinline__ float moe_dot8(const __nv_bfloat16* w, const float* x, float s) {
+  const uint4 u = *reinterpret_cast<const uint4*>(w);
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+  const float4 p = *reinterpret_cast<const float4*>(x), q = *reinterpret_cast<const float4*>(x + 4);
+  const float2 a = __bfloat1622float2(h[0]), b = __bfloat1622float2(h[1]), c = __bfloat1622float2(h[2]), d = __bfloat1622float2(h[3]);
+  s = fmaf(a.x, p.x, s); s = fmaf(a.y, p.y, s); s = fmaf(b.x, p.z, s); s = fmaf(b.y, p.w, s);
+  s = fmaf(c.x, q.x, s); s = fmaf(c.y, q.y, s); s = fmaf(d.x, q.z, s); s = fmaf(d.y, q.w, s);
+  return s;
+}
+
 // grid (ceil(ff / MOE_WARPS), pairs); a warp an output column; x row of the pair's token in shared memory as float32
 template <typename T>
 __global__ void __launch_bounds__(MOE_WARPS * 32)
 moe_gate_up_pairs_kernel(const T* __restrict__ x, const T* __restrict__ wg, const T* __restrict__ wu, const int* __restrict__ ids,
-                         const int* __restrict__ slots, T* __restrict__ h, int top, int d, int ff, int experts, int act) {
-  extern __shared__ float moe_x[];
+                         const int* __restrict__ slots, T* __restrict__ h, int top, int d, int ff, int experts, int act, int vec) {
+  extern __shared__ __align__(16) float moe_x[];
   ms_pdl_trigger();
   ms_pdl_wait();
   const int pair = blockIdx.y, t = pair / top;
@@ -97,10 +115,17 @@ moe_gate_up_pairs_kernel(const T* __restrict__ x, const T* __restrict__ wg, cons
   const T* g = wg + ((size_t)e * ff + n) * d;
   const T* u = wu + ((size_t)e * ff + n) * d;
   float sg = 0.f, su = 0.f;
-  for (int c = lane; c < d; c += 32) {
-    const float xv = moe_x[c];
-    sg = fmaf(ms_to_float(g[c]), xv, sg);
-    su = fmaf(ms_to_float(u[c]), xv, su);
+  if (vec) {  // (the order of a sum depends on d and on this flag, which depends on d and the pointers' alignment alone)
+    for (int c = lane * 8; c < d; c += 256) {
+      sg = moe_dot8(g + c, moe_x + c, sg);
+      su = moe_dot8(u + c, moe_x + c, su);
+    }
+  } else {
+    for (int c = lane; c < d; c += 32) {
+      const float xv = moe_x[c];
+      sg = fmaf(ms_to_float(g[c]), xv, sg);
+      su = fmaf(ms_to_float(u[c]), xv, su);
+    }
   }
   sg = ms_warp_sum(sg);
   su = ms_warp_sum(su);
@@ -111,8 +136,8 @@ moe_gate_up_pairs_kernel(const T* __restrict__ x, const T* __restrict__ wg, cons
 template <typename T>
 __global__ void __launch_bounds__(MOE_WARPS * 32)
 moe_down_pairs_kernel(const T* __restrict__ h, const T* __restrict__ wd, const int* __restrict__ ids, const float* __restrict__ weights,
-                      const int* __restrict__ slots, float* __restrict__ y, int top, int d, int ff, int experts) {
-  extern __shared__ float moe_h[];  // [top][ff]
+                      const int* __restrict__ slots, float* __restrict__ y, int top, int d, int ff, int experts, int vec) {
+  extern __shared__ __align__(16) float moe_h[];  // [top][ff]
   ms_pdl_trigger();
   ms_pdl_wait();
   const int t = blockIdx.y;
@@ -132,7 +157,11 @@ moe_down_pairs_kernel(const T* __restrict__ h, const T* __restrict__ wd, const i
     const T* w = wd + ((size_t)e * d + n) * ff;
     const float* hj = moe_h + (size_t)j * ff;
     float s = 0.f;
-    for (int c = lane; c < ff; c += 32) s = fmaf(ms_to_float(w[c]), hj[c], s);
+    if (vec) {
+      for (int c = lane * 8; c < ff; c += 256) s = moe_dot8(w + c, hj + c, s);
+    } else {
+      for (int c = lane; c < ff; c += 32) s = fmaf(ms_to_float(w[c]), hj[c], s);
+    }
     s = ms_warp_sum(s);
     total = fmaf(weights[(size_t)t * top + j], s, total);
   }
@@ -147,13 +176,14 @@ MS_API int ms_moe_gate_up_pairs(const void* x, const void* wg, const void* wu, c
   MS_REQUIRE((long long)tokens * top <= 65535, "moe_gate_up_pairs: %d pairs are more than one launch takes", tokens * top);
   MS_REQUIRE((size_t)d * 4 <= 48 * 1024, "moe_gate_up_pairs: rows of %d are too wide", d);
   const dim3 grid((ff + MOE_WARPS - 1) / MOE_WARPS, tokens * top), block(MOE_WARPS * 32);
+  const int vec = d % 8 == 0 && ((uintptr_t)wg | (uintptr_t)wu) % 32 == 0;
   if (dtype == MS_F32)
     MS_LAUNCH_RESULT("moe_gate_up_pairs", ms_launch(moe_gate_up_pairs_kernel<float>, grid, block, (size_t)d * 4, stream, 1, true, (const float*)x,
-                                                    (const float*)wg, (const float*)wu, ids, slots, (float*)h, top, d, ff, experts, act));
+                                                    (const float*)wg, (const float*)wu, ids, slots, (float*)h, top, d, ff, experts, act, vec));
   else if (dtype == MS_BF16)
     MS_LAUNCH_RESULT("moe_gate_up_pairs",
                      ms_launch(moe_gate_up_pairs_kernel<__nv_bfloat16>, grid, block, (size_t)d * 4, stream, 1, true, (const __nv_bfloat16*)x,
-                               (const __nv_bfloat16*)wg, (const __nv_bfloat16*)wu, ids, slots, (__nv_bfloat16*)h, top, d, ff, experts, act));
+                               (const __nv_bfloat16*)wg, (const __nv_bfloat16*)wu, ids, slots, (__nv_bfloat16*)h, top, d, ff, experts, act, vec));
   else
     MS_REQUIRE(false, "moe_gate_up_pairs: unknown dtype %d", dtype);
   return 0;
@@ -165,14 +195,22 @@ MS_API int ms_moe_down_pairs(const void* h, const void* wd, const int* ids, cons
   MS_REQUIRE(tokens > 0 && top > 0 && d > 0 && ff > 0 && experts > 0, "moe_down_pairs: bad arguments");
   MS_REQUIRE(tokens <= 65535, "moe_down_pairs: %d tokens are more than one launch takes", tokens);
   const size_t smem = (size_t)top * ff * 4;
-  MS_REQUIRE(smem <= 48 * 1024, "moe_down_pairs: %d experts of %d a token need %zu bytes of shared memory", top, ff, smem);
+  MS_REQUIRE(smem <= 200 * 1024, "moe_down_pairs: %d experts of %d a token need %zu bytes of shared memory", top, ff, smem);
+  static size_t configured = 48 * 1024;
+  if (smem > configured) {
+    cudaError_t e1 = cudaFuncSetAttribute(moe_down_pairs_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e2 = cudaFuncSetAttribute(moe_down_pairs_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    MS_REQUIRE(e1 == cudaSuccess && e2 == cudaSuccess, "moe_down_pairs: cannot get %zu bytes of shared memory", smem);
+    configured = smem;
+  }
   const dim3 grid((d + MOE_WARPS - 1) / MOE_WARPS, tokens), block(MOE_WARPS * 32);
+  const int vec = ff % 8 == 0 && (uintptr_t)wd % 32 == 0;
   if (dtype == MS_F32)
     MS_LAUNCH_RESULT("moe_down_pairs", ms_launch(moe_down_pairs_kernel<float>, grid, block, smem, stream, 1, true, (const float*)h,
-                                                 (const float*)wd, ids, weights, slots, y, top, d, ff, experts));
+                                                 (const float*)wd, ids, weights, slots, y, top, d, ff, experts, vec));
   else if (dtype == MS_BF16)
     MS_LAUNCH_RESULT("moe_down_pairs", ms_launch(moe_down_pairs_kernel<__nv_bfloat16>, grid, block, smem, stream, 1, true,
-                                                 (const __nv_bfloat16*)h, (const __nv_bfloat16*)wd, ids, weights, slots, y, top, d, ff, experts));
+                                                 (const __nv_bfloat16*)h, (const __nv_bfloat16*)wd, ids, weights, slots, y, top, d, ff, experts, vec));
   else
     MS_REQUIRE(false, "moe_down_pairs: unknown dtype %d", dtype);
   return 0;

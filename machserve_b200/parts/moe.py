@@ -20,7 +20,8 @@ class RoutedExperts(FeedForward):
     """
 
     graph_safe = True
-    GROUPED_FROM_ROWS = 17  # fewer rows stream the chosen experts' rows pair by pair (decoding)
+    GROUPED_FROM_ROWS = 17  # fewer rows stream the chosen experts' rows pair by pair (decoding) ...
+    GROUPED_FROM_BYTES = 1 << 30  # ... unless the pairs would read this much: sorted, an expert's matrices are read once
 
     def __init__(self, spec):
         super().__init__(spec)
@@ -51,6 +52,7 @@ class RoutedExperts(FeedForward):
         self.b_router = vector_f32(tensors[p + "router.b"]) if self.router_bias else None
         stack = lambda name: matrix(torch.stack([tensors[f"{p}e{e}.{name}"] for e in range(self.experts)], dim=0), rt)
         self.w_gate, self.w_up, self.w_down = stack("gate"), stack("up"), stack("down")
+        self.expert_bytes = 3 * self.inter * self.hidden * self.w_gate.element_size()
         self.grouped = rt.dtype == torch.bfloat16 and ops.moe_grouped_supports(self.hidden, self.inter, self.experts)
 
     def forward(self, ctx, x):
@@ -63,7 +65,8 @@ class RoutedExperts(FeedForward):
         ops.moe_route(logits, self.top, ids, weights)
         h = ws.get("moe.h", (t * self.top, self.inter), rt.dtype)
         delta = ws.get("ffn.delta_f32", (t, self.hidden), torch.float32)
-        if self.grouped and t >= self.GROUPED_FROM_ROWS and t * self.top // 64 + self.experts <= 65535:
+        many = t >= self.GROUPED_FROM_ROWS or t * self.top * self.expert_bytes >= self.GROUPED_FROM_BYTES
+        if self.grouped and many and t * self.top // 128 + self.experts <= 65535:
             # many rows: sorted by expert on the device, every expert's rows in tiles on the tensor cores
             scratch = ws.get("moe.sorted", (ops.moe_grouped_scratch_ints(t * self.top, self.experts),), torch.int32)
             z = ws.get("moe.z", (t * self.top, self.hidden), torch.float32)
