@@ -806,14 +806,14 @@ def time_fozutar_kernels(torch, ops, raw, pk):
     kw, vw = heads * dk, heads * dv
     state = torch.zeros(b, heads, dk, dv, device=dev)
     proj = rnd(n, 2 * kw + 2 * vw + 16, scale=0.1)
-    dec = -torch.rand(n, kw, device=dev, generator=g) * 0.1
+    dec = torch.exp(-torch.rand(n, kw, device=dev, generator=g) * 0.1)
     og = torch.empty(n, vw, device=dev)
     cu1 = torch.arange(b + 1, dtype=torch.int32, device=dev)
     t_new = us(lambda: ops.gla_scan(proj[:b], 0, kw, 2 * kw, dec[:b], 0.1, state, cu1, slotd, slotd, og[:b], b, heads, dk, dv))
     entry("gla_scan_decode", t_new, nbytes=2 * b * heads * dk * dv * 4)
     cup = torch.tensor([0, n], dtype=torch.int32, device=dev)
     zero = torch.zeros(n, dtype=torch.int32, device=dev)
-    t_new = us(lambda: ops.gla_scan(proj, 0, kw, 2 * kw, dec, 0.1, state, cup, zero[:1], zero, og, 1, heads, dk, dv), reps=2)
+    t_new = us(lambda: ops.gla_scan(proj, 0, kw, 2 * kw, dec, 0.1, state, cup, zero[:1], zero, og, 1, heads, dk, dv, narrow=True), reps=2)
     entry("gla_scan_prefill", t_new, flops=n * heads * dk * dv * 4)  # (CUDA-core multiply-adds: the scan is sequential)
     w2 = rnd(kw, 16, dt=bf)
     y = torch.empty(n, vw, dtype=bf, device=dev)

@@ -82,7 +82,7 @@ class _Signatures:
     ms_attention_wide_scored = [P, P, P, P, I, P, P, P, P, I, I, I, I, I, I, I, I, I, I, F, F, P, I, I, I, P]
     ms_attention_wide_mma_scored = [P, P, P, P, P, P, P, P, I, I, P, P, I, I, I, I, I, I, I, I, I, F, I, P, F, P, I, I, P]
     ms_gla_decay = [P, I, P, I, P, I, F, P, I, I, P]
-    ms_gla_scan = [P, I, I, I, I, P, F, P, P, P, P, P, I, I, I, I, P]
+    ms_gla_scan = [P, I, I, I, I, P, F, P, P, P, P, P, I, I, I, I, I, P]
     ms_gla_output = [P, P, I, P, F, P, I, I, I, I, P]
     ms_moe_route = [P, I, I, P, P, I, P]
     ms_moe_gate_up_pairs = [P, P, P, P, P, P, I, I, I, I, I, I, I, P]
@@ -1221,7 +1221,7 @@ def head_norm_store(proj, eps: float, positions, slot_of_token, block_table, q_o
 
 
 def gla_decay(u, w2, b2, tau: float, out):
-    """out[t, n] = logsigmoid(w2[n, :] . u[t, :] + b2[n]) / tau: the logarithm of the decay sigmoid(z)^(1/tau), in float32.
+    """out[t, n] = exp(logsigmoid(w2[n, :] . u[t, :] + b2[n]) / tau): the decay sigmoid(z)^(1/tau), through its logarithm, in float32.
     u float32 [T, rank] (unit column stride); w2 [n, rank] float32 or bfloat16; b2 float32 [n] or None; out float32 [T, n]."""
     t, n = out.shape
     rank = w2.shape[1]
@@ -1232,20 +1232,22 @@ def gla_decay(u, w2, b2, tau: float, out):
     return out
 
 
-def gla_scan(proj, q_off: int, k_off: int, v_off: int, log_decay, q_scale: float, state, cu_tokens, state_slots, slot_of_token, out,
-             seqs: int, heads: int, dk: int, dv: int):
-    """The recurrence S <- diag(exp(g_t)) S + k_t v_t^T, o_t = S^T (q_t * q_scale), per sequence and head, over the rows of the
+def gla_scan(proj, q_off: int, k_off: int, v_off: int, decay, q_scale: float, state, cu_tokens, state_slots, slot_of_token, out,
+             seqs: int, heads: int, dk: int, dv: int, narrow: bool = False):
+    """The recurrence S <- diag(a_t) S + k_t v_t^T, o_t = S^T (q_t * q_scale), per sequence and head, over the rows of the
     step in order, from and to `state` (float32 [slots, heads, dk, dv]; a sequence's slot is state_slots[s]).
-    proj float32 [T, ld] holds q, k (heads*dk each) and v (heads*dv) at the column offsets; log_decay float32 [T, heads*dk];
-    out float32 [T, heads*dv]; cu_tokens int32 [seqs + 1]; rows whose slot_of_token is negative are passed over."""
-    _need(proj.dtype == torch.float32 and proj.stride(1) == 1 and log_decay.dtype == torch.float32 and log_decay.is_contiguous()
+    proj float32 [T, ld] holds q, k (heads*dk each) and v (heads*dv) at the column offsets; decay (a) float32 [T, heads*dk];
+    out float32 [T, heads*dv]; cu_tokens int32 [seqs + 1]; rows whose slot_of_token is negative are passed over.
+    `narrow`: blocks of 8 value columns instead of 32 (more blocks a sequence: for steps with long portions); same bits."""
+    _need(proj.dtype == torch.float32 and proj.stride(1) == 1 and decay.dtype == torch.float32 and decay.is_contiguous()
           and out.dtype == torch.float32 and out.is_contiguous() and state.dtype == torch.float32 and state.is_contiguous(),
           "gla_scan: bad layout")
-    _need(tuple(state.shape[1:]) == (heads, dk, dv) and log_decay.shape[1] == heads * dk and out.shape[1] == heads * dv,
+    _need(tuple(state.shape[1:]) == (heads, dk, dv) and decay.shape[1] == heads * dk and out.shape[1] == heads * dv,
           "gla_scan: bad shapes")
     _need(cu_tokens.numel() >= seqs + 1 and state_slots.numel() >= seqs, "gla_scan: bad sequence lists")
-    _check(lib().ms_gla_scan(_ptr(proj), proj.stride(0), int(q_off), int(k_off), int(v_off), _ptr(log_decay), float(q_scale), _ptr(state),
-                             _ptr(cu_tokens), _ptr(state_slots), _ptr(slot_of_token), _ptr(out), int(seqs), heads, dk, dv, _stream()),
+    _check(lib().ms_gla_scan(_ptr(proj), proj.stride(0), int(q_off), int(k_off), int(v_off), _ptr(decay), float(q_scale), _ptr(state),
+                             _ptr(cu_tokens), _ptr(state_slots), _ptr(slot_of_token), _ptr(out), int(seqs), heads, dk, dv, int(narrow),
+                             _stream()),
            "gla_scan")
     return out
 

@@ -18,7 +18,7 @@ class GatedLinearAttention(Mixer):
     with S [key_dim, value_dim] zero at the start of a sequence, float32, carried from step to step in the request's state
     slot.  Each head's o_t is divided by its root mean square over value_dim (eps inside the root) and multiplied by a weight
     [value_dim] that the heads share; the heads side by side are multiplied by silu(Wg x) and go through Wo.  The five input
-    projections are one product with a float32 result; the decay's logarithm, its exponential, the state, the norm and the
+    projections are one product with a float32 result; the decay (through its logarithm), the state, the norm and the
     gate are float32.
 
     params: prefix, hidden_size, num_heads, key_dim, value_dim, decay_rank, tau, eps.  Tensors under the prefix: q, k, v, g,
@@ -69,11 +69,11 @@ class GatedLinearAttention(Mixer):
         ws = rt.workspace
         proj = ws.get("gla.proj", (t, self.width), torch.float32)
         ops.linear(x, self.w_in, None, proj)
-        decay = ws.get("gla.log_decay", (t, self.kw), torch.float32)
+        decay = ws.get("gla.decay", (t, self.kw), torch.float32)
         ops.gla_decay(proj[:, self.a_off:], self.w_a2, self.b_a2, self.tau, decay)
         o = ws.get("gla.o", (t, self.vw), torch.float32)
         ops.gla_scan(proj, self.q_off, self.k_off, self.v_off, decay, self.dk ** -0.5, cache.state, ctx.cu_tokens, ctx.state_slots,
-                     ctx.slot_of_token, o, ctx.num_seqs, self.heads, self.dk, self.dv)
+                     ctx.slot_of_token, o, ctx.num_seqs, self.heads, self.dk, self.dv, narrow=ctx.max_query_len > 16)
         y = ws.get("gla.y", (t, self.vw), rt.dtype)
         ops.gla_output(o, proj[:, self.g_off:self.g_off + self.vw], self.norm, self.eps, y, self.heads, self.dv)
         delta = ws.get("mixer.delta_f32", (t, self.hidden), torch.float32)

@@ -370,12 +370,19 @@ def test_a_far_key_lives_on_in_the_state():
     while at < n:
         m = min(sizes.pop(0) if sizes else 64, n - at)
         o = torch.empty((m, vw), dtype=torch.float32, device="cuda")
-        ops.gla_scan(_dev(proj[at : at + m]), 0, kw, 2 * kw, _dev(g[at : at + m]), 1.0, state, _dev(np.array([0, m], dtype=np.int32)),
-                     _dev(np.zeros(1, dtype=np.int32)), _dev(np.zeros(m, dtype=np.int32)), o, 1, heads, dk, dv)
+        ops.gla_scan(_dev(proj[at : at + m]), 0, kw, 2 * kw, _dev(np.exp(g[at : at + m])), 1.0, state, _dev(np.array([0, m], dtype=np.int32)),
+                     _dev(np.zeros(1, dtype=np.int32)), _dev(np.zeros(m, dtype=np.int32)), o, 1, heads, dk, dv, narrow=m > 16)
         got[at : at + m] = o.cpu().numpy()
         at += m
     # (600 decays of 1 - 1e-4 multiplied up in float32: a few parts in 100,000; a lost or doubled state would be all of it)
     assert_close(got, want.reshape(n, -1), 1e-4, "rows in portions and alone against the whole sequence")
+    # blocks of 32 and of 8 value columns: the same bits, whole or in portions
+    for narrow in (False, True):
+        state.zero_()
+        o = torch.empty((n, vw), dtype=torch.float32, device="cuda")
+        ops.gla_scan(_dev(proj), 0, kw, 2 * kw, _dev(np.exp(g)), 1.0, state, _dev(np.array([0, n], dtype=np.int32)), _dev(np.zeros(1, dtype=np.int32)),
+                     _dev(np.zeros(n, dtype=np.int32)), o, 1, heads, dk, dv, narrow=narrow)
+        assert np.array_equal(o.cpu().numpy(), got.astype(np.float32)), "the scan's result must not depend on how the rows were cut"
 
 
 @pytest.mark.parametrize("experts,top,d,ff", [(5, 2, 64, 32), (3, 3, 50, 21), (7, 1, 48, 40), (12, 4, 96, 24)])
