@@ -145,8 +145,7 @@ gla_scan_kernel(const float* __restrict__ proj, int ld, int q_off, int k_off, in
     if (t0 + GLA_TB < rows) request(t0 + GLA_TB, stg ^ 1);
     asm volatile("cp.async.commit_group;\n" ::);
     float* base = stage0 + (size_t)stg * GLA_TB * ROW;
-#pragma unroll 2
-    for (int tb = 0; tb < nt; ++tb) {
+    auto token = [&](int tb) {
       const float* t = base + (size_t)tb * ROW;
       const float v = t[3 * KP + c];
       float acc0 = 0.f, acc1 = 0.f;  // two chains of sums (even and odd rows), added at the end: the order is fixed
@@ -178,6 +177,12 @@ gla_scan_kernel(const float* __restrict__ proj, int ld, int q_off, int k_off, in
         }
       }
       part[((size_t)tb * GLA_GROUPS + grp) * COLS + c] = acc0 + acc1;
+    };
+    if (nt == GLA_TB) {  // a full batch: unrolled, so that the loads of later tokens are on their way under the sums of earlier ones
+#pragma unroll
+      for (int tb = 0; tb < GLA_TB; ++tb) token(tb);
+    } else {
+      for (int tb = 0; tb < nt; ++tb) token(tb);
     }
     __syncthreads();
     for (int tb = grp; tb < nt; tb += GLA_GROUPS) {
