@@ -135,9 +135,42 @@ def library_path(verbose: bool = True, flavor=None) -> Path:
             fcntl.flock(lock, fcntl.LOCK_UN)
 
 
-def _compile(out: Path, lib: Path, verbose: bool, flags) -> None:
+def library_for(stems, verbose: bool = True, flavor=None) -> Path:
+    """A library that holds at least the kernels of the source files named by `stems` (file names without `.cu`): the
+    whole library when it is there and current (a tree that came with it, or an earlier whole build), else a library of
+    those files alone, built now if it is not there yet.  A model whose parts say which files they need waits for those
+    at its first use and for no others.  `stems` None: the whole library."""
+    if stems is None:
+        return library_path(verbose, flavor)
+    fp = _fingerprint(flavor)
+    in_tree = CSRC / _folder(flavor)
+    if (in_tree / LIB_NAME).is_file() and (in_tree / "stamp").is_file() and (in_tree / "stamp").read_text() == fp:
+        return in_tree / LIB_NAME
+    known = {p.stem for p in sources()}
+    stems = sorted(set(stems))
+    unknown = [x for x in stems if x not in known]
+    if unknown:
+        raise BuildError(f"no such kernel files: {', '.join(unknown)}")
+    out = build_dir(flavor)
+    if (out / LIB_NAME).is_file() and (out / "stamp").is_file() and (out / "stamp").read_text() == fp:
+        return out / LIB_NAME
+    key = hashlib.sha256((fp + "," + ",".join(stems)).encode()).hexdigest()[:12]  # (fp covers every source and the flags)
+    lib = out / f"{LIB_NAME[:-3]}_{key}.so"
+    if lib.is_file():
+        return lib
+    with open(out / "lock", "w") as lock:
+        fcntl.flock(lock, fcntl.LOCK_EX)
+        try:
+            if not lib.is_file():
+                _compile(out, lib, verbose, _flags(flavor), only=stems)
+            return lib
+        finally:
+            fcntl.flock(lock, fcntl.LOCK_UN)
+
+
+def _compile(out: Path, lib: Path, verbose: bool, flags, only=None) -> None:
     nvcc = find_nvcc()
-    srcs = sources()
+    srcs = sources() if only is None else [p for p in sources() if p.stem in set(only)]
     if not srcs:
         raise BuildError(f"no .cu files under {CSRC}")
     t0 = time.time()

@@ -116,13 +116,15 @@ class ModelRunner:
         self.dtype = parse_dtype(dtype)
         self.device = torch.device(device)
         torch.cuda.set_device(self.device)
-        ops.lib()  # fail now, loudly, if the kernels cannot be built or loaded
         self.spec = config.model_spec()
         self.max_seq_len = int(max_seq_len or min(self.spec.max_positions, page_size * num_pages))
         self.page_size, self.max_requests, self.max_step_tokens = page_size, max_requests, max_step_tokens
         self.rt = Runtime(self.dtype, self.device, Workspace(self.device), self.max_seq_len,
                           torch.cuda.get_device_properties(self.device).multi_processor_count)
         self.model = DecoderModel(self.spec)
+        # fail now, loudly, if the kernels cannot be built or loaded; a model whose parts name their kernel files waits for
+        # the compilation of those alone
+        ops.require(self.model.kernel_files())
         # before anything is allocated: does it fit?  (weights that are on the device already are not needed twice)
         plan = estimate_device_bytes(self.model, self.dtype, page_size, num_pages, max_requests, self.max_seq_len)
         resident = sum(t.numel() * t.element_size() for t in tensors.values() if t.is_cuda)

@@ -23,8 +23,12 @@ class KernelError(RuntimeError):
     pass
 
 
-_lib = None
+_lib = None      # the loaded library (ctypes), behind `_proxy`
+_files = None    # the source files whose kernels it holds: a set, or ALL
 _flavor = None
+ALL = "all"
+# what every model needs whatever its parts: the error channel and launch switch, the stream's own kernels, the products
+CORE_FILES = ("elementwise", "gemm_f32", "gemm_small_m")
 
 
 def use_flavor(flavor) -> None:
@@ -35,23 +39,69 @@ def use_flavor(flavor) -> None:
     _flavor = flavor
 
 
-def lib():
-    """The loaded kernel library (built on first use)."""
+def _load(path) -> None:
     global _lib
-    if _lib is None:
-        path = _build.library_path(flavor=_flavor)
-        try:
-            L = ctypes.CDLL(str(path))
-        except OSError as e:
-            raise KernelError(f"the kernel library {path} could not be loaded: {e}") from None
-        L.ms_last_error.restype = ctypes.c_char_p
-        for name in dir(_Signatures):
-            if name.startswith("ms_"):
+    try:
+        L = ctypes.CDLL(str(path))
+    except OSError as e:
+        raise KernelError(f"the kernel library {path} could not be loaded: {e}") from None
+    L.ms_last_error.restype = ctypes.c_char_p
+    for name in dir(_Signatures):
+        if name.startswith("ms_"):
+            try:
                 fn = getattr(L, name)
-                fn.argtypes = getattr(_Signatures, name)
-                fn.restype = c_int
-        _lib = L
-    return _lib
+            except AttributeError:
+                continue  # a library of some of the files
+            fn.argtypes = getattr(_Signatures, name)
+            fn.restype = c_int
+    L._ms_path = str(path)
+    _lib = L
+
+
+def require(files=None) -> None:
+    """Makes sure that the loaded library holds the kernels of the named source files (names without `.cu`; None: of all
+    files), building it first if need be.  A model's runner names the files its parts declare (`Part.kernel_files`), so that
+    the first use of a model waits for the compilation of what it needs and of nothing else; where the whole library is
+    there already, it is loaded whatever is asked.  A later call that asks for more loads a library of both."""
+    global _files
+    if _lib is not None and (_files == ALL or (files is not None and set(files) <= _files)):
+        return
+    want = None
+    if files is not None:
+        want = set(files) | set(CORE_FILES) | (_files if isinstance(_files, set) else set())
+    path = _build.library_for(sorted(want) if want is not None else None, flavor=_flavor)
+    _load(path)
+    _files = ALL if want is None or path.name == _build.LIB_NAME else want
+
+
+def has(name: str) -> bool:
+    """Whether the loaded library holds the entry point `name` (a library of some of the files may not)."""
+    return _lib is not None and hasattr(_lib, name)
+
+
+class _Proxy:
+    """The loaded library; an entry point that a library of some of the files lacks brings in the whole library."""
+
+    def __getattr__(self, name):
+        if _lib is None:
+            require(None)
+        try:
+            return getattr(_lib, name)
+        except AttributeError:
+            if _files == ALL:
+                raise
+            require(None)
+            return getattr(_lib, name)
+
+
+_proxy = _Proxy()
+
+
+def lib():
+    """The loaded kernel library (built on first use: the whole of it, unless `require` named files before)."""
+    if _lib is None:
+        require(None)
+    return _proxy
 
 
 def set_pdl(on: bool) -> None:
@@ -60,7 +110,8 @@ def set_pdl(on: bool) -> None:
 
 
 def library_file() -> str:
-    return str(_build.library_path(flavor=_flavor))
+    lib()
+    return _lib._ms_path
 
 
 class _Signatures:
@@ -793,7 +844,10 @@ def gemm_tc_status(reset: bool = True) -> int:
 def tc_status_codes(reset: bool = True):
     """(code of the tcgen05 products, code of the tcgen05 attention): both are read, and cleared with `reset`,
     whichever of them is set.  Synchronizes."""
-    return int(lib().ms_gemm_tc_status(1 if reset else 0)), int(lib().ms_attention_tc_status(1 if reset else 0))
+    lib()  # (kernels that are not in the loaded library cannot have given up a wait)
+    gemm = int(_lib.ms_gemm_tc_status(1 if reset else 0)) if has("ms_gemm_tc_status") else 0
+    attention = int(_lib.ms_attention_tc_status(1 if reset else 0)) if has("ms_attention_tc_status") else 0
+    return gemm, attention
 
 
 def tc_wait_probe(kernel: str, polls: int = 1000) -> None:

@@ -233,6 +233,10 @@ class Part:
     # step may be captured once in a CUDA graph and replayed.  A part that loops on the host over the
     # step's sequences, or reads host-side lists of the context, leaves this False.
     graph_safe = False
+    # The kernel source files (names under csrc/ without `.cu`) whose entry points the part calls, beyond those every
+    # model needs (`ops.CORE_FILES`); None: not said, which stands for all files.  A model all of whose parts say it
+    # waits at its first use for the compilation of those files alone.
+    kernel_files = None
 
     def __init__(self, spec: PartSpec):
         self.spec = spec
@@ -383,6 +387,7 @@ class Block:
     accepts_row_stats = False
     accepts_pairs = False  # True: `pending` may also be a `DeltaPair`
     optional_feed_forward = False  # True: the block also arranges a layer that has no feed-forward
+    kernel_files = ()  # what the block itself launches beyond its parts' kernels (see `Part.kernel_files`)
 
     def __init__(self, spec: LayerSpec, mixer: Mixer, feed_forward: Optional[FeedForward], mixer_norm: Norm, ff_norm: Optional[Norm]):
         self.spec, self.mixer, self.feed_forward, self.mixer_norm, self.ff_norm = spec, mixer, feed_forward, mixer_norm, ff_norm

@@ -24,6 +24,7 @@ class PreNormBlock(Block):
 
     graph_safe = True
     accepts_row_stats = True
+    kernel_files = None  # (its parts' few-row path: not said)
 
     def bind(self, tensors, rt):
         super().bind(tensors, rt)

@@ -46,6 +46,7 @@ class ChunkedAttention(wide_attend.WideAttendPlan, Mixer):
     """
 
     graph_safe = True
+    kernel_files = ('head_norm_store', 'attention_wide', 'attention_wide_mma')
 
     def __init__(self, spec):
         super().__init__(spec)

@@ -43,6 +43,7 @@ class ScaledPositionEmbedding(TokenEmbedding):
     """
 
     graph_safe = True
+    kernel_files = ('stream',)
 
     def __init__(self, spec):
         super().__init__(spec)
@@ -80,6 +81,7 @@ class LMHead(Head):
     """
 
     graph_safe = True
+    kernel_files = ()
 
     def __init__(self, spec):
         super().__init__(spec)

@@ -26,6 +26,7 @@ class GatedLinearAttention(Mixer):
     """
 
     graph_safe = True
+    kernel_files = ('gla',)
 
     def __init__(self, spec):
         super().__init__(spec)

@@ -142,6 +142,7 @@ class GatedMLP(FeedForward):
     """
 
     graph_safe = True
+    kernel_files = ('stream',)
 
     def __init__(self, spec):
         super().__init__(spec)

@@ -75,6 +75,16 @@ class DecoderModel:
             needs.append(need)
         return needs
 
+    def kernel_files(self):
+        """The kernel source files the model's parts call (`Part.kernel_files`), or None if some part does not say."""
+        out = set()
+        for p in [*self.parts(), *self.blocks]:
+            files = getattr(p, "kernel_files", None)
+            if files is None:
+                return None
+            out.update(files)
+        return sorted(out)
+
     def graph_safe(self) -> bool:
         """Whether a decoding step of this model may be captured in a CUDA graph: every part says so."""
         return all(p.graph_safe for p in self.parts()) and all(getattr(b, "graph_safe", False) for b in self.blocks)

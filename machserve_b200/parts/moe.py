@@ -20,6 +20,7 @@ class RoutedExperts(FeedForward):
     """
 
     graph_safe = True
+    kernel_files = ('moe', 'moe_grouped')
     GROUPED_FROM_ROWS = 17  # fewer rows stream the chosen experts' rows pair by pair (decoding) ...
     GROUPED_FROM_BYTES = 1 << 30  # ... unless the pairs would read this much: sorted, an expert's matrices are read once
 

@@ -15,6 +15,7 @@ class RMSNorm(Norm):
     """
 
     graph_safe = True
+    kernel_files = ('stream',)
     accepts_pairs = True  # a `DeltaPair` is summed and added by a kernel of its own (x + (a + b), float32)
 
     def __init__(self, spec):

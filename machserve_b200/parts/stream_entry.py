@@ -57,6 +57,7 @@ class AddEmbedding(StreamEntry):
     """
 
     graph_safe = True
+    kernel_files = ('stream',)
 
     def __init__(self, spec):
         super().__init__(spec)

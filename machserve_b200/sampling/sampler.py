@@ -24,6 +24,7 @@ class Sampler:
     def __init__(self, max_rows: int, device):
         max_rows += max_rows % 2  # the 64-bit states lie behind three blocks of max_rows 32-bit values
         self.max_rows, self.device = max_rows, device
+        ops.require(("sampling",))  # (a library of some of the kernel files may be loaded: the sampler's file joins it)
         # one pinned staging block: temperature f32 | top_p f32 | top_k i32 | rng i64 (as 2 x i32)
         # (three in turn, each guarded by an event: the copy of one batch's options may still be queued on the
         # device when the host fills in the next batch's)
