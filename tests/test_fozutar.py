@@ -165,3 +165,28 @@ def test_plain_router_takes_the_largest():
     assert ids.tolist() == [[1, 2]]
     e = np.exp([0.9, 0.8])
     assert np.allclose(weights[0], e / e.sum()), "the softmax is over the chosen logits only"
+
+
+def test_a_library_of_some_of_the_kernel_files(tmp_path, monkeypatch):
+    """A model whose parts name their kernel files is built a library of those files alone (when the whole library is not
+    there): here the smallest such library, by the compiler, without a GPU."""
+    import ctypes
+    import shutil
+
+    from machserve_b200.csrc import build
+
+    if shutil.which("nvcc") is None and not (build.Path("/usr/local/cuda/bin/nvcc")).is_file():
+        pytest.skip("no nvcc")
+    cfg = config_from_json(CASES["A"]["config"])
+    files = DecoderModel(cfg.model_spec()).kernel_files()
+    assert files == ["attention_wide", "attention_wide_mma", "gla", "head_norm_store", "moe", "moe_grouped", "stream"]
+    fp = build._fingerprint()
+    monkeypatch.setattr(build, "_fingerprint", lambda flavor=None: fp + "x")  # as if no current library were anywhere
+    monkeypatch.setenv("MACHSERVE_B200_BUILD_DIR", str(tmp_path))
+    lib = build.library_for(["elementwise", "stream"], verbose=False)
+    assert lib.parent == tmp_path and lib.name != build.LIB_NAME
+    loaded = ctypes.CDLL(str(lib))
+    assert hasattr(loaded, "ms_gated_act_mul") and hasattr(loaded, "ms_last_error") and not hasattr(loaded, "ms_gla_scan")
+    assert build.library_for(["stream", "elementwise"], verbose=False) == lib, "the same files: the same library, not built again"
+    with pytest.raises(build.BuildError, match="no such kernel files"):
+        build.library_for(["no_such_file"], verbose=False)
