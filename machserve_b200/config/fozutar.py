@@ -4,7 +4,8 @@ config.json names the design under `architecture` and gives `vocab`, `width`, `m
 `embedding.scale`, the list `layers` and, optionally, `loop`.  Every layer is a parallel one with ONE RMS norm that its
 mixer and its feed-forward both read, and names its mixer under `type` with that mixer's sizes under `mixer`:
 
-* `attention`: heads, kv_heads, dim (query/key size per head), vdim, scale, softcap, bias_max, mask {size}.  Grouped heads
+* `attention`: heads, kv_heads (heads if absent), dim (query/key size per head), vdim, scale, softcap (none if absent),
+  bias_max, mask {size} (every earlier key if absent).  Grouped heads
   with q and k biases, the values are the projected keys, every head normed on its own, a soft cap on the scores, a
   learned bias by distance (table `rel`), a mask by chunks of mask.size positions, no rotation.
 * `gla`: heads, dim (key channels per head), vdim, tau.  Gated linear attention with a low-rank decay projection.
@@ -38,26 +39,33 @@ class ChunkedAttentionSizes:
     dim: int
     vdim: int
     scale: float
-    softcap: float
+    softcap: Optional[float]
     bias_max: int
-    chunk: int
+    chunk: Optional[int]  # None: every earlier key is visible
     bias_rows: Optional[int] = None  # rows of the bias table: from the tensor `rel` when config.json does not say
 
     @classmethod
     def read(cls, r: JsonReader) -> "ChunkedAttentionSizes":
-        heads, kv = r.integer("heads"), r.integer("kv_heads")
+        heads = r.integer("heads")
+        kv = r.integer("kv_heads", heads)
         if heads % kv:
             raise ConfigError(f"{r.where}: heads {heads} is not a multiple of kv_heads {kv}")
-        dim, vdim = r.integer("dim"), r.integer("vdim")
+        dim = r.integer("dim")
+        vdim = r.integer("vdim", dim)
         if vdim != dim:
             raise ConfigError(f"{r.where}: the values are the keys, so vdim {vdim} must equal dim {dim}")
-        mask = _sub(r.raw, "mask", r.where)
-        return cls(heads, kv, dim, vdim, r.number("scale"), r.number("softcap"), r.integer("bias_max", minimum=2),
-                   mask.integer("size"), r.optional_integer("bias_rows", minimum=2))
+        mask = _sub(r.raw, "mask", r.where, required=False)
+        softcap = r.number("softcap") if r.raw.get("softcap") is not None else None
+        return cls(heads, kv, dim, vdim, r.number("scale"), softcap, r.integer("bias_max", minimum=2),
+                   mask.integer("size") if mask else None, r.optional_integer("bias_rows", minimum=2))
 
     def to_json(self) -> Dict[str, Any]:
         out = {"heads": self.heads, "kv_heads": self.kv_heads, "dim": self.dim, "vdim": self.vdim, "scale": self.scale,
-               "softcap": self.softcap, "bias_max": self.bias_max, "mask": {"size": self.chunk}}
+               "bias_max": self.bias_max}
+        if self.softcap is not None:
+            out["softcap"] = self.softcap
+        if self.chunk is not None:
+            out["mask"] = {"size": self.chunk}
         if self.bias_rows is not None:
             out["bias_rows"] = self.bias_rows
         return out

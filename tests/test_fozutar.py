@@ -68,6 +68,21 @@ def test_sizes_that_only_the_tensors_give(tmp_path):
     assert load_config(d) == full
 
 
+def test_optional_keys_of_the_attention():
+    raw = copy.deepcopy(CASES["A"]["config"])
+    m = raw["layers"][1]["mixer"]
+    for key in ("softcap", "mask", "kv_heads"):
+        m.pop(key)
+    cfg = config_from_json(raw)
+    a = cfg.layers[1].mixer
+    assert a.softcap is None and a.chunk is None and a.kv_heads == a.heads
+    assert type(cfg).from_json(cfg.to_json()) == cfg
+    spec = cfg.model_spec().layers[1].mixer
+    assert spec["softcap"] is None and spec["chunk"] is None
+    need = DecoderModel(cfg.model_spec()).cache_needs()[1]
+    assert need.chunk is None and need.window is None
+
+
 def test_run_order_follows_the_loop():
     cfg = config_from_json(CASES["A"]["config"])
     runs = cfg.model_spec().run_order
@@ -112,7 +127,7 @@ def test_cache_groups_states_and_chunks():
     (lambda c: c["layers"][0]["mlp"]["router"].__setitem__("top", 9), "more than"),
     (lambda c: c["loop"].__setitem__("stop", 9), "range"),
     (lambda c: c.pop("width"), "'width' is required"),
-    (lambda c: c["layers"][1]["mixer"].pop("softcap"), "'softcap' is required"),
+    (lambda c: c["layers"][1]["mixer"].pop("scale"), "'scale' is required"),
     (lambda c: c["layers"][0]["mixer"].pop("tau"), "'tau' is required"),
 ])
 def test_config_errors_name_the_key(change, message):
