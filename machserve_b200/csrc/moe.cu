@@ -1,6 +1,6 @@
 // A routed feed-forward (mixture of experts): the router's choice, and the experts' products for (token, expert) pairs.
 //
-//   route:    of a token's E router logits (float32) the `top` largest are chosen (the lower index wins a tie); their
+//   route:    of a token's E router logits (float32, plus the router's bias) the `top` largest are chosen (the lower index wins a tie); their
 //             weights are the softmax over the chosen logits only.  ids int32 [T, top], weights float32 [T, top], in
 //             descending order of the logits.  One warp a token.
 //   gate_up:  h[p, n] = act(Wg[e_p][n, :] . x[t_p, :]) * (Wu[e_p][n, :] . x[t_p, :]) for pair p = (token t_p, its j-th expert e_p)
@@ -12,7 +12,8 @@
 #include "launch.cuh"
 
 __global__ void __launch_bounds__(128)
-moe_route_kernel(const float* __restrict__ logits, int experts, int top, int* __restrict__ ids, float* __restrict__ weights, int tokens) {
+moe_route_kernel(const float* __restrict__ logits, const float* __restrict__ bias, int experts, int top, int* __restrict__ ids,
+                 float* __restrict__ weights, int tokens) {
   ms_pdl_trigger();
   ms_pdl_wait();
   const int lane = threadIdx.x & 31;
@@ -27,7 +28,7 @@ moe_route_kernel(const float* __restrict__ logits, int experts, int top, int* __
     float best = -INFINITY;
     int best_i = 0x7fffffff;
     for (int e = lane; e < experts; e += 32) {
-      const float v = z[e];
+      const float v = z[e] + (bias ? bias[e] : 0.f);
       // after (last_v, last_i) in the order: larger value first, lower index first among equals
       const bool after = v < last_v || (v == last_v && e > last_i);
       if (after && (v > best || (v == best && e < best_i))) {
@@ -59,11 +60,13 @@ moe_route_kernel(const float* __restrict__ logits, int experts, int top, int* __
     for (int j = 0; j < top; ++j) weights[(size_t)t * top + j] /= sum;
 }
 
-MS_API int ms_moe_route(const float* logits, int experts, int top, int* ids, float* weights, int tokens, cudaStream_t stream) {
+// logits float32 [tokens, experts]; bias float32 [experts] or null (added to the logits before the choice)
+MS_API int ms_moe_route(const float* logits, const float* bias, int experts, int top, int* ids, float* weights, int tokens,
+                        cudaStream_t stream) {
   if (tokens == 0) return 0;
   MS_REQUIRE(tokens > 0 && experts > 0 && top > 0 && top <= experts, "moe_route: bad arguments tokens=%d experts=%d top=%d", tokens, experts, top);
-  MS_LAUNCH_RESULT("moe_route", ms_launch(moe_route_kernel, dim3((tokens + 3) / 4), dim3(128), 0, stream, 1, true, logits, experts, top, ids,
-                                          weights, tokens));
+  MS_LAUNCH_RESULT("moe_route", ms_launch(moe_route_kernel, dim3((tokens + 3) / 4), dim3(128), 0, stream, 1, true, logits, bias, experts, top,
+                                          ids, weights, tokens));
   return 0;
 }
 

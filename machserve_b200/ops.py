@@ -129,13 +129,13 @@ class _Signatures:
     ms_embed_scaled_pos = [P, I, P, P, P, P, I, I, I, I, F, P]
     ms_add_streams_rmsnorm = [P, P, I, P, I, P, P, P, P, I, P, I, I, F, P]
     ms_gated_act_mul = [P, I, P, I, I, I, I, P]
-    ms_head_norm_store = [P, I, P, P, F, I, P, P, P, I, I, I, P, P, P, P, I, I, I, I, I, I, I, I, P]
+    ms_head_norm_store = [P, I, P, P, P, F, I, P, P, P, I, I, I, P, P, P, P, I, I, I, I, I, I, I, I, P]
     ms_attention_wide_scored = [P, P, P, P, I, P, P, P, P, I, I, I, I, I, I, I, I, I, I, F, F, P, I, I, I, P]
     ms_attention_wide_mma_scored = [P, P, P, P, P, P, P, P, I, I, P, P, I, I, I, I, I, I, I, I, I, F, I, P, F, P, I, I, P]
     ms_gla_decay = [P, I, P, I, P, I, F, P, I, I, P]
     ms_gla_scan = [P, I, I, I, I, P, F, P, P, P, P, P, I, I, I, I, I, P]
     ms_gla_output = [P, P, I, P, F, P, I, I, I, I, P]
-    ms_moe_route = [P, I, I, P, P, I, P]
+    ms_moe_route = [P, P, I, I, P, P, I, P]
     ms_moe_gate_up_pairs = [P, P, P, P, P, P, I, I, I, I, I, I, I, P]
     ms_moe_down_pairs = [P, P, P, P, P, P, I, I, I, I, I, I, P]
     ms_moe_grouped = [P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, P]
@@ -1246,11 +1246,13 @@ def gated_act_mul(gate_up, out, activation: str):
 
 
 def head_norm_store(proj, eps: float, positions, slot_of_token, block_table, q_out, k_pages, v_pages, num_heads: int, num_kv_heads: int,
-                    dk: int, dv: int, v_off: Optional[int], norm: bool = True, wq=None, wk=None, store: bool = True, q_half=None):
+                    dk: int, dv: int, v_off: Optional[int], norm: bool = True, wq=None, wk=None, store: bool = True, q_half=None,
+                    bias=None):
     """Every query head and every key head divided by its own root mean square over dk (eps inside the root; optional
     weights wq, wk float32 [dk]; `norm` False leaves them as they are); q to q_out (float32 [T, Hq*dk]) and, optionally, to
     a bfloat16 copy; the normed keys into k_pages; into v_pages the values at column `v_off` of the product, or, `v_off`
-    None, the keys as they were projected (before the norm).  proj float32 [T, >= (Hq + Hkv)*dk (+ Hkv*dv)] = [q | k | v]."""
+    None, the keys as they were projected (before the norm).  proj float32 [T, >= (Hq + Hkv)*dk (+ Hkv*dv)] = [q | k | v];
+    `bias` (float32, one entry per column that is read, or None) is added to the product first."""
     t = q_out.shape[0]
     _need(proj.dtype == torch.float32 and proj.stride(1) == 1 and q_out.dtype == torch.float32 and q_out.is_contiguous()
           and q_out.numel() == t * num_heads * dk, "head_norm_store: bad layout")
@@ -1258,15 +1260,17 @@ def head_norm_store(proj, eps: float, positions, slot_of_token, block_table, q_o
           "head_norm_store: bad bfloat16 copy of the queries")
     for w in (wq, wk):
         _need(w is None or (w.dtype == torch.float32 and w.numel() == dk and w.is_contiguous()), "head_norm_store: bad norm weight")
+    width = (num_heads + num_kv_heads) * dk + (0 if v_off is None else num_kv_heads * dv)
+    _need(bias is None or (bias.dtype == torch.float32 and bias.is_contiguous() and bias.numel() >= width), "head_norm_store: bad bias")
     if store:
         _need(k_pages.is_contiguous() and v_pages.is_contiguous() and k_pages.dtype == v_pages.dtype
               and tuple(k_pages.shape[1:]) == (num_kv_heads, k_pages.shape[2], dk)
               and tuple(v_pages.shape[1:]) == (num_kv_heads, k_pages.shape[2], dv), "head_norm_store: bad pages")
         _need(block_table.dtype == torch.int32 and block_table.is_contiguous(), "head_norm_store: bad block table")
     _check(lib().ms_head_norm_store(
-        _ptr(proj), proj.stride(0), _ptr(wq), _ptr(wk), float(eps), int(norm), _ptr(positions), _ptr(slot_of_token), _ptr(block_table),
-        block_table.shape[1] if store else 0, k_pages.shape[0] if store else 0, k_pages.shape[2] if store else 0, _ptr(q_out),
-        _ptr(q_half), _ptr(k_pages if store else None), _ptr(v_pages if store else None), _code(k_pages) if store else F32, t,
+        _ptr(proj), proj.stride(0), _ptr(bias), _ptr(wq), _ptr(wk), float(eps), int(norm), _ptr(positions), _ptr(slot_of_token),
+        _ptr(block_table), block_table.shape[1] if store else 0, k_pages.shape[0] if store else 0, k_pages.shape[2] if store else 0,
+        _ptr(q_out), _ptr(q_half), _ptr(k_pages if store else None), _ptr(v_pages if store else None), _code(k_pages) if store else F32, t,
         num_heads, num_kv_heads, dk, dv, -1 if v_off is None else int(v_off), int(store), _stream()), "head_norm_store")
     return q_out
 
@@ -1322,14 +1326,15 @@ def gla_output(o, gate, weight, eps: float, out, heads: int, dv: int):
 # ------------------------------------------------------------------------------------------------ routed feed-forward
 
 
-def moe_route(logits, top: int, ids, weights):
-    """Of each row's router logits (float32 [T, E]) the `top` largest (the lower index wins a tie), in descending order:
+def moe_route(logits, top: int, ids, weights, bias=None):
+    """Of each row's router logits (float32 [T, E], plus `bias` float32 [E] if given) the `top` largest (the lower index wins a tie), in descending order:
     ids int32 [T, top], weights float32 [T, top] = the softmax over the chosen logits only."""
     t, e = logits.shape
     _need(logits.dtype == torch.float32 and logits.is_contiguous() and ids.dtype == torch.int32 and ids.is_contiguous()
           and weights.dtype == torch.float32 and weights.is_contiguous() and tuple(ids.shape) == (t, top) and tuple(weights.shape) == (t, top),
           "moe_route: bad arguments")
-    _check(lib().ms_moe_route(_ptr(logits), e, int(top), _ptr(ids), _ptr(weights), t, _stream()), "moe_route")
+    _need(bias is None or (bias.dtype == torch.float32 and bias.is_contiguous() and bias.numel() == e), "moe_route: bad bias")
+    _check(lib().ms_moe_route(_ptr(logits), _ptr(bias), e, int(top), _ptr(ids), _ptr(weights), t, _stream()), "moe_route")
     return ids, weights
 
 

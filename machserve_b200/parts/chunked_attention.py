@@ -117,12 +117,13 @@ class ChunkedAttention(wide_attend.WideAttendPlan, Mixer):
         ws = rt.workspace
         width = self.qw + (self.kw + self.vw if owns_cache else 0)
         proj = ws.get("chunked_attn.qkv", (t, width), torch.float32)
-        ops.linear(x, self.w_in[:width], self.b_in[:width] if self.b_in is not None else None, proj)
+        ops.linear(x, self.w_in[:width], None, proj)  # (the biases are added where the product is read)
         q = ws.get("chunked_attn.q", (t, self.qw), torch.float32)
         k_pages, v_pages = cache.planes["k"], cache.planes["v"]
         table = cache.block_table(ctx)
         ops.head_norm_store(proj, self.eps, ctx.positions, ctx.slot_of_token, table, q, k_pages, v_pages, self.hq, self.hkv, self.dk,
-                            self.dv, None if self.values_are_keys else self.qw + self.kw, norm=self.head_norm, store=owns_cache)
+                            self.dv, None if self.values_are_keys else self.qw + self.kw, norm=self.head_norm, store=owns_cache,
+                            bias=self.b_in)
         out = ws.get("chunked_attn.out", (t, self.hq * self.dv), rt.dtype)
         wide_attend.attend(ctx, rt, self.fast, table, q, k_pages, v_pages, out, None, self.hq, self.hkv, self.dk, self.dv, None,
                            self.scale, score=self.score)

@@ -60,10 +60,10 @@ class RoutedExperts(FeedForward):
         rt, t = self.rt, x.shape[0]
         ws = rt.workspace
         logits = ws.get("moe.logits", (t, self.experts), torch.float32)
-        ops.linear(x, self.w_router, self.b_router, logits)
+        ops.linear(x, self.w_router, None, logits)  # (the router's bias is added where the logits are read)
         ids = ws.get("moe.ids", (t, self.top), torch.int32)
         weights = ws.get("moe.weights", (t, self.top), torch.float32)
-        ops.moe_route(logits, self.top, ids, weights)
+        ops.moe_route(logits, self.top, ids, weights, self.b_router)
         h = ws.get("moe.h", (t * self.top, self.inter), rt.dtype)
         delta = ws.get("ffn.delta_f32", (t, self.hidden), torch.float32)
         many = t >= self.GROUPED_FROM_ROWS or t * self.top * self.expert_bytes >= self.GROUPED_FROM_BYTES

@@ -143,8 +143,11 @@ def test_heads_normed_alone_and_values_that_are_the_keys(dtype):
     pages, table = _paged(rng, [31], hkv, dk, page)
     kp, vp = _dev(pages, cache_dtype), _dev(pages, cache_dtype)
     q = torch.empty((5, hq * dk), dtype=torch.float32, device="cuda")
-    ops.head_norm_store(_dev(proj), eps, _dev(positions), _dev(np.zeros(5, dtype=np.int32)), _dev(table), q, kp, vp, hq, hkv, dk, dk, None)
+    bias = rng.normal(size=(hq + hkv) * dk).astype(np.float32)  # (the projections' biases are added where the product is read)
+    ops.head_norm_store(_dev(proj), eps, _dev(positions), _dev(np.zeros(5, dtype=np.int32)), _dev(table), q, kp, vp, hq, hkv, dk, dk, None,
+                        bias=_dev(bias))
     p64 = proj.astype(np.float64)
+    p64[:, : (hq + hkv) * dk] += bias
     assert_close(q.cpu().numpy(), plain.unit_rms(p64[:, : hq * dk].reshape(5, hq, dk), eps).reshape(5, -1), 2e-6, "queries")
     k = p64[:, hq * dk : (hq + hkv) * dk].reshape(5, hkv, dk)
     tol = 2e-6 if dtype == "float32" else 8e-3
@@ -402,9 +405,10 @@ def test_router_and_experts(experts, top, d, ff, dtype):
     logits = seen(h) @ w["router"].T + w["router.b"]
     ids = torch.empty((t, top), dtype=torch.int32, device="cuda")
     weights = torch.empty((t, top), dtype=torch.float32, device="cuda")
-    ops.moe_route(_dev(logits.astype(np.float32)), top, ids, weights)
-    w_route = {"router": np.eye(experts), "router.b": np.zeros(experts)}
-    want_ids, want_w = plain.route(logits.astype(np.float32).astype(np.float64), w_route, "", top)
+    rb = rng.normal(size=experts).astype(np.float32)  # (the router's bias is added where the logits are read)
+    ops.moe_route(_dev((logits - rb).astype(np.float32)), top, ids, weights, _dev(rb))
+    w_route = {"router": np.eye(experts), "router.b": rb.astype(np.float64)}
+    want_ids, want_w = plain.route((logits - rb).astype(np.float32).astype(np.float64), w_route, "", top)
     assert np.array_equal(ids.cpu().numpy(), want_ids)
     assert_close(weights.cpu().numpy(), want_w, 2e-6, "softmax over the chosen logits")
     stack = lambda name: _dev(np.stack([w[f"e{e}.{name}"] for e in range(experts)]).astype(np.float32), rt)
