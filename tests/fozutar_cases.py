@@ -68,6 +68,16 @@ CASES = {
         {**_gla(3, 7, 9, 3.0, 3), "mlp": _moe(21, 5, 2)},
         {**_attention(5, 1, 5, 0.45, 7.0, 7, 25, 13), "mlp": _dense(37)},
     ], (1, 2, 2)), seed=25, page=8),
+    # recurrent layers only (no pages at all), the whole model looped twice
+    "F": dict(config=_config(120, 32, 1e-5, 4.0, 256, [
+        {**_gla(2, 8, 16, 12.0, 4), "mlp": _dense(64)},
+        {**_gla(1, 16, 8, 6.0, 2), "mlp": _moe(32, 4, 2)},
+    ], (0, 2, 2)), seed=26, page=8),
+    # attention layers only (no state at all), no loop
+    "G": dict(config=_config(90, 48, 1e-6, 1.5, 256, [
+        {**_attention(3, 1, 16, 0.25, 8.0, 10, 60, 24), "mlp": _moe(32, 4, 1)},
+        {**_attention(2, 2, 8, 0.4, 40.0, 4, 20, 10), "mlp": _dense(96)},
+    ]), seed=27, page=16),
 }
 
 
