@@ -40,7 +40,7 @@ class ChunkedAttentionSizes:
     vdim: int
     scale: float
     softcap: Optional[float]
-    bias_max: int
+    bias_max: float
     chunk: Optional[int]  # None: every earlier key is visible
     bias_rows: Optional[int] = None  # rows of the bias table: from the tensor `rel` when config.json does not say
 
@@ -56,7 +56,7 @@ class ChunkedAttentionSizes:
             raise ConfigError(f"{r.where}: the values are the keys, so vdim {vdim} must equal dim {dim}")
         mask = _sub(r.raw, "mask", r.where, required=False)
         softcap = r.number("softcap") if r.raw.get("softcap") is not None else None
-        return cls(heads, kv, dim, vdim, r.number("scale"), softcap, r.integer("bias_max", minimum=2),
+        return cls(heads, kv, dim, vdim, r.number("scale"), softcap, r.number("bias_max"),
                    mask.integer("size") if mask else None, r.optional_integer("bias_rows", minimum=2))
 
     def to_json(self) -> Dict[str, Any]:

@@ -13,7 +13,7 @@ from ..weights.loader import TensorDecl
 from .base import CachePlane, Mixer, PagedCache, matrix, register_mixer, vector_f32
 
 
-def distance_bucket(n: int, rows: int, reach: int) -> int:
+def distance_bucket(n: int, rows: int, reach: float) -> int:
     """The row of a bias table of `rows` rows that distance n >= 0 reads: the first half of the rows one distance each, the
     other half spaced evenly in the logarithm of the distance up to `reach`, the last row for everything beyond."""
     half = rows // 2
@@ -22,7 +22,7 @@ def distance_bucket(n: int, rows: int, reach: int) -> int:
     return min(rows - 1, half + int(math.floor(math.log(n / half) / math.log(reach / half) * (rows - half))))
 
 
-def bias_by_distance(table: torch.Tensor, reach: int, longest: int) -> torch.Tensor:
+def bias_by_distance(table: torch.Tensor, reach: float, longest: int) -> torch.Tensor:
     """table [rows, heads] -> float32 [heads, longest]: entry [h, n] is the bias of head h at distance n (the kernels clamp
     larger distances to the last entry, which by then is the table's last row or `longest` covers every distance)."""
     rows = table.shape[0]
@@ -105,7 +105,7 @@ class ChunkedAttention(wide_attend.WideAttendPlan, Mixer):
         if self.bias_rows is not None:
             # one entry per distance a query can see: within a chunk, or up to the longest sequence
             longest = min(self.chunk or self.max_positions, self.max_positions, rt.max_positions)
-            dist = bias_by_distance(tensors[p + "rel"].detach().to("cpu"), int(self.bias_reach), max(1, longest)).to(rt.device)
+            dist = bias_by_distance(tensors[p + "rel"].detach().to("cpu"), float(self.bias_reach), max(1, longest)).to(rt.device)
         self.dist_bias = dist
         self.score = None
         if self.softcap or dist is not None or self.chunk:
