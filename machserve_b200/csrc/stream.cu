@@ -98,21 +98,15 @@ add_streams_rmsnorm_kernel(float* __restrict__ residual, const void* __restrict_
     for (int i = 0; i < ST_KEEP; ++i) {
       const int g = threadIdx.x + i * ST_THREADS;
       if (g < ngroups) {
+        // every load is requested before the first is used: one round trip to memory, not one per stream
+        const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
         float4 x = *reinterpret_cast<const float4*>(residual + base + 4 * g);
-        float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (a) s = st_load4(a, a_dtype, base + 4 * g);
-        if (b) {
-          const float4 t = st_load4(b, b_dtype, base + 4 * g);
-          s.x += t.x; s.y += t.y; s.z += t.z; s.w += t.w;
-        }
-        if (first) {
-          const float4 t = *reinterpret_cast<const float4*>(first + base + 4 * g);
-          s.x += t.x; s.y += t.y; s.z += t.z; s.w += t.w;
-        }
-        if (vec) {
-          const float4 t = *reinterpret_cast<const float4*>(vec + 4 * g);
-          s.x += t.x; s.y += t.y; s.z += t.z; s.w += t.w;
-        }
+        const float4 ta = a ? st_load4(a, a_dtype, base + 4 * g) : zero;
+        const float4 tb = b ? st_load4(b, b_dtype, base + 4 * g) : zero;
+        const float4 tf = first ? *reinterpret_cast<const float4*>(first + base + 4 * g) : zero;
+        const float4 tv = vec ? *reinterpret_cast<const float4*>(vec + 4 * g) : zero;
+        float4 s = make_float4(((ta.x + tb.x) + tf.x) + tv.x, ((ta.y + tb.y) + tf.y) + tv.y, ((ta.z + tb.z) + tf.z) + tv.z,
+                               ((ta.w + tb.w) + tf.w) + tv.w);
         x.x += s.x; x.y += s.y; x.z += s.z; x.w += s.w;
         if (adds && !rows) *reinterpret_cast<float4*>(residual + base + 4 * g) = x;
         v[i] = x;
